@@ -1,0 +1,363 @@
+// Fused multi-head attention for sm_100a, head_dim 64, fp16 / bf16:
+//   out = softmax(Q.K^T / sqrt(d) + mask) . V        per (batch, head)
+// on the packed QKV Gemm output [tokens, 3, heads, 64].  Replaces the vendored
+// FusedMHARunnerFP16v2 (precompiled sm_70..sm_89 cubins) that the reference layer calls at
+// lib/Kernels/GPU/LLM.cu:79-81; masks: key padding from per-sequence lengths and, optionally,
+// causal.
+//
+// One CTA handles 128 queries of one (batch, head) and walks the keys in tiles of 128
+// (flash-style online softmax; tiles that are fully masked are skipped):
+//   warp 4, one thread   TMA loads of the Q / K / V tiles (128 x 64, 128-byte swizzle) and
+//                        the two tcgen05.mma groups per key tile:
+//                          S = Q.K^T   (M=128, N=128, K=64)  -> TMEM columns [0,128)
+//                          O_t = P.V   (M=128, N=64, K=128)  -> TMEM columns [128,192)
+//                        V is used as it lies in memory (keys x head_dim, an MN-major B
+//                        operand), so no transpose pass is needed.
+//   warps 0-3            one thread per query row: tcgen05.ld the scores, running max and
+//                        sum in fp32 (exp2 with log2(e)/sqrt(d) folded in), P written to
+//                        shared memory as the 16-bit A operand of the second MMA, then the
+//                        partial product O_t is read back and accumulated in registers
+//                        with the usual rescaling.
+// Shared memory is 80 KiB and TMEM 256 columns per CTA, so two CTAs share an SM and
+// overlap each other's load / MMA / softmax phases.  Every wait is bounded.
+#include <type_traits>
+
+#include "ops_common.h"
+#include "ptx_sm100.cuh"
+
+namespace mdc {
+
+namespace attn {
+constexpr int BQ = 128, BKV = 128, D = 64;
+constexpr int TILE_BYTES = 128 * D * 2;  // 16 KiB: one 128 x 64 16-bit tile
+constexpr int P_BYTES = 2 * TILE_BYTES;  // 128 x 128 P as two 128 x 64 k-blocks
+constexpr int THREADS = 160;
+constexpr int TMEM_COLS = 256;
+constexpr int S_COL = 0, O_COL = 128;
+constexpr size_t SMEM_BYTES = 3 * TILE_BYTES + P_BYTES + 1024;
+}  // namespace attn
+
+struct AttnParams {
+  const int32_t *seq_lens;  // [batch] or nullptr
+  void *out;                // [batch*seq, heads*64]
+  int batch, seq, heads;
+  int causal;
+  float scale_log2e;  // log2(e) / sqrt(d)
+  uint32_t *err;
+};
+
+template <typename T16>
+__device__ __forceinline__ uint32_t pack16(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack16<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack16<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
+template <typename T16>
+__global__ void __launch_bounds__(attn::THREADS, 2)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnParams p) {
+  using namespace attn;
+  using namespace ptx;
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ uint64_t bar_q, bar_k, bar_v, bar_s_full, bar_p_ready, bar_o_full;
+  __shared__ uint32_t tmem_slot;
+  __shared__ uint32_t abort_flag_s;
+  volatile uint32_t *abort_flag = &abort_flag_s;
+
+  uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+  uint8_t *sQ = tiles, *sK = tiles + TILE_BYTES, *sV = tiles + 2 * TILE_BYTES, *sP = tiles + 3 * TILE_BYTES;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_tile = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+  const int q0 = q_tile * BQ;
+  const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.seq) : p.seq;
+  // keys this query tile can see: [0, kv_end)
+  int kv_end = len;
+  if (p.causal) kv_end = min(kv_end, q0 + BQ);
+  const int n_kv = (kv_end + BKV - 1) / BKV;
+  const int hd = p.heads * D;
+  const int row_base = b * p.seq;  // first token row of this sequence in the packed tensor
+
+  if (threadIdx.x == 0) {
+    abort_flag_s = 0;
+    tma_prefetch_desc(&tmap_qkv);
+    mbar_init(&bar_q, 1);
+    mbar_init(&bar_k, 1);
+    mbar_init(&bar_v, 1);
+    mbar_init(&bar_s_full, 1);
+    mbar_init(&bar_p_ready, 128);
+    mbar_init(&bar_o_full, 1);
+    mbar_init_fence();
+  }
+  if (warp == 4) {
+    tmem_alloc(&tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------ loads + MMA issue ------------------------------
+    if (lane == 0 && n_kv > 0) {
+      constexpr bool kBf16 = std::is_same<T16, __nv_bfloat16>::value;
+      constexpr uint32_t idesc_s = make_idesc_f16(BQ, BKV, kBf16, false, false);
+      constexpr uint32_t idesc_o = make_idesc_f16(BQ, D, kBf16, false, true);  // V is MN-major
+      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV),
+                     p_addr = smem_u32(sP);
+      mbar_arrive_expect_tx(&bar_q, TILE_BYTES);
+      tma_load_2d(sQ, &tmap_qkv, &bar_q, head * D, row_base + q0);
+      mbar_arrive_expect_tx(&bar_k, TILE_BYTES);
+      tma_load_2d(sK, &tmap_qkv, &bar_k, hd + head * D, row_base);
+      mbar_arrive_expect_tx(&bar_v, TILE_BYTES);
+      tma_load_2d(sV, &tmap_qkv, &bar_v, 2 * hd + head * D, row_base);
+      uint32_t code = 0;
+      if (!mbar_wait(&bar_q, 0, abort_flag)) code = 0x51000000u;
+      for (int j = 0; j < n_kv && !code; ++j) {
+        const uint32_t ph = j & 1;
+        if (j > 0) {
+          // S columns are free once the softmax warps have consumed tile j-1 (they arrived
+          // on bar_p_ready, which this thread already waited for); V of tile j can be
+          // fetched once the previous P.V has finished reading the V and P buffers.
+          if (!mbar_wait(&bar_o_full, ph ^ 1, abort_flag)) { code = 0x52000000u | j; break; }
+          mbar_arrive_expect_tx(&bar_v, TILE_BYTES);
+          tma_load_2d(sV, &tmap_qkv, &bar_v, 2 * hd + head * D, row_base + j * BKV);
+        }
+        if (!mbar_wait(&bar_k, ph, abort_flag)) { code = 0x53000000u | j; break; }
+        tc_fence_after();
+        {
+          const uint64_t a_desc = make_smem_desc_sw128(q_addr, 16, 1024);
+          const uint64_t b_desc = make_smem_desc_sw128(k_addr, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k)
+            umma_f16_ss(tmem_base + S_COL, a_desc + 2 * k, b_desc + 2 * k, idesc_s, k != 0);
+        }
+        umma_commit(&bar_s_full);
+        if (!mbar_wait(&bar_s_full, ph, abort_flag)) { code = 0x54000000u | j; break; }
+        if (j + 1 < n_kv) {  // K buffer is free again: prefetch the next key tile
+          mbar_arrive_expect_tx(&bar_k, TILE_BYTES);
+          tma_load_2d(sK, &tmap_qkv, &bar_k, hd + head * D, row_base + (j + 1) * BKV);
+        }
+        if (!mbar_wait(&bar_p_ready, ph, abort_flag)) { code = 0x55000000u | j; break; }
+        if (!mbar_wait(&bar_v, ph, abort_flag)) { code = 0x56000000u | j; break; }
+        tc_fence_after();
+        {
+#pragma unroll
+          for (int k = 0; k < BKV / 16; ++k) {
+            // A: P, K-major, k-block (k / 4) of 64 keys, 32 bytes per 16 keys inside it.
+            const uint64_t a_desc =
+                make_smem_desc_sw128(p_addr + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024);
+            // B: V as loaded (key rows of 128 bytes): 16 keys = 2048 bytes further.
+            const uint64_t b_desc = make_smem_desc_sw128(v_addr + k * 2048, 1024, 1024);
+            umma_f16_ss(tmem_base + O_COL, a_desc, b_desc, idesc_o, k != 0);
+          }
+        }
+        umma_commit(&bar_o_full);
+      }
+      if (code) atomicCAS(p.err, 0u, code);
+    }
+  } else {
+    // ------------------------------ softmax + output ------------------------------
+    const int r = threadIdx.x;  // query row inside the tile == TMEM lane
+    const int q_local = q0 + r;  // query index inside the sequence
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    float o_acc[D];
+#pragma unroll
+    for (int e = 0; e < D; ++e) o_acc[e] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const uint32_t ph = j & 1;
+      if (!mbar_wait(&bar_s_full, ph, abort_flag)) {
+        atomicCAS(p.err, 0u, 0x61000000u | j);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      // columns (keys) this row may attend to inside the tile: [0, ncol)
+      int ncol = kv_end - j * BKV;
+      if (p.causal) ncol = min(ncol, q_local + 1 - j * BKV);
+      ncol = max(min(ncol, BKV), 0);
+      // pass 1: row maximum
+      float m_tile = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t s[32];
+        tmem_ld_32x32(tmem_base + lane_addr + S_COL + c * 32, s);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c * 32 + i < ncol) m_tile = fmaxf(m_tile, __uint_as_float(s[i]));
+      }
+      const float m_new = fmaxf(m_run, m_tile);
+      // rows with no visible key yet keep m = -inf; use 0 as the reference point then
+      const float m_ref = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = m_run == -INFINITY ? 0.f : exp2f((m_run - m_ref) * p.scale_log2e);
+      // fold in the previous tile's partial product before P is overwritten
+      if (j > 0) {
+        if (!mbar_wait(&bar_o_full, ph ^ 1, abort_flag)) {
+          atomicCAS(p.err, 0u, 0x62000000u | j);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_base + lane_addr + O_COL + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha_prev, __uint_as_float(o[i]));
+        }
+      }
+      // pass 2: P = exp2((s - m) * c), row sum, 16-bit P into swizzled shared memory
+      float l_tile = 0.f;
+      const float mc = m_ref * p.scale_log2e;
+#pragma unroll 1
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t s[32];
+        tmem_ld_32x32(tmem_base + lane_addr + S_COL + c * 32, s);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = 0.f, p1 = 0.f;
+          if (c * 32 + i < ncol) p0 = exp2f(fmaf(__uint_as_float(s[i]), p.scale_log2e, -mc));
+          if (c * 32 + i + 1 < ncol) p1 = exp2f(fmaf(__uint_as_float(s[i + 1]), p.scale_log2e, -mc));
+          l_tile += p0 + p1;
+          packed[i >> 1] = pack16<T16>(p0, p1);
+        }
+        // 32 keys = four 16-byte chunks of row r in k-block (c / 2); chunk index is
+        // XOR-swizzled with the row (128-byte swizzle, same pattern TMA writes)
+        uint8_t *blk = sP + (c >> 1) * TILE_BYTES + r * 128;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = (c & 1) * 4 + q;
+          *reinterpret_cast<uint4 *>(blk + ((chunk ^ (r & 7)) << 4)) =
+              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        }
+      }
+      l_run = fmaf(l_run, alpha, l_tile);
+      m_run = m_new;
+      alpha_prev = alpha;
+      // P visible to the tensor core (async proxy); S reads of this tile are complete
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bar_p_ready);
+    }
+    if (ok && n_kv > 0) {
+      const uint32_t ph = (n_kv - 1) & 1;
+      if (!mbar_wait(&bar_o_full, ph, abort_flag)) {
+        atomicCAS(p.err, 0u, 0x63000000u);
+        ok = false;
+      } else {
+        tc_fence_after();
+        // the last tile's own alpha was already applied to l_run; O needs alpha_prev
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_base + lane_addr + O_COL + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha_prev, __uint_as_float(o[i]));
+        }
+      }
+    }
+    if (ok && q_local < p.seq) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      T16 *dst = static_cast<T16 *>(p.out) + static_cast<size_t>(row_base + q_local) * hd + head * D;
+#pragma unroll
+      for (int g = 0; g < D / 8; ++g) {
+        uint4 o;
+        o.x = pack16<T16>(o_acc[8 * g + 0] * inv, o_acc[8 * g + 1] * inv);
+        o.y = pack16<T16>(o_acc[8 * g + 2] * inv, o_acc[8 * g + 3] * inv);
+        o.z = pack16<T16>(o_acc[8 * g + 4] * inv, o_acc[8 * g + 5] * inv);
+        o.w = pack16<T16>(o_acc[8 * g + 6] * inv, o_acc[8 * g + 7] * inv);
+        reinterpret_cast<uint4 *>(dst)[g] = o;
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 4) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+bool encode_tmap_2d(CUtensorMap *map, const void *base, int32_t dtype, uint64_t inner, uint64_t outer,
+                    uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
+
+}  // namespace mdc
+
+using namespace mdc;
+
+MDC_API void mgpuAttention(const void *qkv, const int32_t *seq_lens, void *out, int64_t batch,
+                           int64_t seq_len, int64_t heads, int64_t head_dim, bool causal,
+                           int32_t dtype, void *stream) {
+  if (batch <= 0 || seq_len <= 0 || heads <= 0) return;
+  const DeviceInfo &di = device_info();
+  if (!di.ok) return;
+  if (head_dim != attn::D) { fail("mgpuAttention: head_dim must be 64"); return; }
+  if (!dtype_is16(dtype)) { fail("mgpuAttention: dtype must be F16 or BF16"); return; }
+  if ((reinterpret_cast<uintptr_t>(qkv) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u)) {
+    fail("mgpuAttention: buffers must be 16-byte aligned");
+    return;
+  }
+  const int64_t tokens = batch * seq_len;
+  const int64_t q_tiles = (seq_len + attn::BQ - 1) / attn::BQ;
+  if (tokens > 0x7fffffff || heads > 65535 || batch > 65535) { fail("mgpuAttention: shape too large"); return; }
+  uint32_t *err = device_error_slot();
+  if (!err) return;
+  CUtensorMap tm;
+  const uint64_t row_elems = static_cast<uint64_t>(3 * heads * attn::D);
+  if (!encode_tmap_2d(&tm, qkv, dtype, row_elems, static_cast<uint64_t>(tokens), row_elems * 2, attn::D, 128))
+    return;
+  AttnParams p;
+  p.seq_lens = seq_lens;
+  p.out = out;
+  p.batch = static_cast<int>(batch);
+  p.seq = static_cast<int>(seq_len);
+  p.heads = static_cast<int>(heads);
+  p.causal = causal ? 1 : 0;
+  p.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(attn::D));
+  p.err = err;
+  dim3 grid(static_cast<unsigned>(q_tiles), static_cast<unsigned>(heads), static_cast<unsigned>(batch));
+  cudaStream_t s = as_stream(stream);
+  if (dtype == MGPU_DTYPE_F16) {
+    auto kern = attention_tcgen05_kernel<__half>;
+    static bool set = false;
+    if (!set) {
+      if (!check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(attn::SMEM_BYTES)), "cudaFuncSetAttribute(attention)"))
+        return;
+      set = true;
+    }
+    kern<<<grid, attn::THREADS, attn::SMEM_BYTES, s>>>(tm, p);
+  } else {
+    auto kern = attention_tcgen05_kernel<__nv_bfloat16>;
+    static bool set = false;
+    if (!set) {
+      if (!check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(attn::SMEM_BYTES)), "cudaFuncSetAttribute(attention)"))
+        return;
+      set = true;
+    }
+    kern<<<grid, attn::THREADS, attn::SMEM_BYTES, s>>>(tm, p);
+  }
+  launched("attention_tcgen05_kernel");
+}

@@ -1,0 +1,265 @@
+// Entry points for the HBM-bound elementwise ops: Add / bias / activation (fp32), element
+// type casts and the one-time weight packing (cast + transpose) for the tensor-core Gemm.
+#include "elementwise_kernels.cuh"
+#include "ops_common.h"
+
+namespace mdc {
+
+std::atomic<uint64_t> g_launch_count{0};
+
+const DeviceInfo &device_info() {
+  static thread_local DeviceInfo info;
+  if (info.ok) return info;
+  int dev = -1;
+  if (!check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return info;
+  cudaDeviceProp p;
+  if (!check_cuda(cudaGetDeviceProperties(&p, dev), "cudaGetDeviceProperties")) return info;
+  info.device = dev;
+  info.sms = p.multiProcessorCount;
+  info.cc_major = p.major;
+  info.cc_minor = p.minor;
+  if (p.major != 10) {
+    fail("this library is built for sm_100a (Blackwell B200) only");
+    return info;
+  }
+  info.ok = true;
+  return info;
+}
+
+// ---- casts -------------------------------------------------------------------------
+template <typename T>
+struct Vec8;  // eight 16-bit elements = 16 bytes
+template <>
+struct Vec8<__half> {
+  __half2 v[4];
+};
+template <>
+struct Vec8<__nv_bfloat16> {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ __half2 pack2(float a, float b, __half) { return __floats2half2_rn(a, b); }
+__device__ __forceinline__ __nv_bfloat162 pack2(float a, float b, __nv_bfloat16) {
+  return __floats2bfloat162_rn(a, b);
+}
+__device__ __forceinline__ float2 unpack2(__half2 v) { return __half22float2(v); }
+__device__ __forceinline__ float2 unpack2(__nv_bfloat162 v) { return __bfloat1622float2(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(float v) { return v; }
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+
+// fp32 -> 16-bit: two float4 in, one 16-byte store out per item.
+template <typename T16>
+__global__ void __launch_bounds__(kEwBlock)
+cast_f32_to_16(const float *__restrict__ src, T16 *__restrict__ dst, int64_t n) {
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  if (aligned16(src) && aligned16(dst)) {
+    const int64_t nvec = n >> 3;
+    const float4 *s4 = reinterpret_cast<const float4 *>(src);
+    Vec8<T16> *d8 = reinterpret_cast<Vec8<T16> *>(dst);
+    for (int64_t i = tid; i < nvec; i += nthreads) {
+      const float4 a = __ldcs(s4 + 2 * i), b = __ldcs(s4 + 2 * i + 1);
+      Vec8<T16> o;
+      o.v[0] = pack2(a.x, a.y, T16());
+      o.v[1] = pack2(a.z, a.w, T16());
+      o.v[2] = pack2(b.x, b.y, T16());
+      o.v[3] = pack2(b.z, b.w, T16());
+      d8[i] = o;
+    }
+    for (int64_t j = (nvec << 3) + tid; j < n; j += nthreads) dst[j] = from_f32<T16>(src[j]);
+  } else {
+    for (int64_t j = tid; j < n; j += nthreads) dst[j] = from_f32<T16>(src[j]);
+  }
+}
+
+template <typename T16>
+__global__ void __launch_bounds__(kEwBlock)
+cast_16_to_f32(const T16 *__restrict__ src, float *__restrict__ dst, int64_t n) {
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  if (aligned16(src) && aligned16(dst)) {
+    const int64_t nvec = n >> 3;
+    const Vec8<T16> *s8 = reinterpret_cast<const Vec8<T16> *>(src);
+    float4 *d4 = reinterpret_cast<float4 *>(dst);
+    for (int64_t i = tid; i < nvec; i += nthreads) {
+      const Vec8<T16> v = s8[i];
+      const float2 a = unpack2(v.v[0]), b = unpack2(v.v[1]), c = unpack2(v.v[2]), d = unpack2(v.v[3]);
+      __stcs(d4 + 2 * i, make_float4(a.x, a.y, b.x, b.y));
+      __stcs(d4 + 2 * i + 1, make_float4(c.x, c.y, d.x, d.y));
+    }
+    for (int64_t j = (nvec << 3) + tid; j < n; j += nthreads) dst[j] = to_f32(src[j]);
+  } else {
+    for (int64_t j = tid; j < n; j += nthreads) dst[j] = to_f32(src[j]);
+  }
+}
+
+template <typename TS, typename TD>
+__global__ void __launch_bounds__(kEwBlock)
+cast_generic(const TS *__restrict__ src, TD *__restrict__ dst, int64_t n) {
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t j = tid; j < n; j += nthreads) dst[j] = from_f32<TD>(to_f32(src[j]));
+}
+
+// fp32 [R, C] -> 16-bit [R, Cp], columns C..Cp-1 zero (row padding for the Gemm's A operand
+// when C is not a multiple of 8).
+template <typename T16>
+__global__ void __launch_bounds__(kEwBlock)
+cast_pad_rows(const float *__restrict__ src, T16 *__restrict__ dst, int64_t R, int64_t C, int64_t Cp) {
+  const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t n = R * Cp;
+  for (int64_t j = tid; j < n; j += nthreads) {
+    const int64_t r = j / Cp, c = j - r * Cp;
+    dst[j] = from_f32<T16>(c < C ? src[r * C + c] : 0.f);
+  }
+}
+
+// weight fp32 [K, N] (N contiguous) -> 16-bit [N, Kp] (K contiguous), zero padded to Kp.
+// 32x32 tiles through shared memory so both the reads and the writes are coalesced.
+template <typename T16>
+__global__ void __launch_bounds__(256)
+pack_weight_kernel(const float *__restrict__ w, T16 *__restrict__ out, int64_t K, int64_t N, int64_t Kp) {
+  __shared__ float tile[32][33];
+  const int64_t k0 = static_cast<int64_t>(blockIdx.y) * 32;
+  const int64_t n0 = static_cast<int64_t>(blockIdx.x) * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+#pragma unroll
+  for (int r = ty; r < 32; r += 8) {
+    const int64_t k = k0 + r, n = n0 + tx;
+    tile[r][tx] = (k < K && n < N) ? w[k * N + n] : 0.f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = ty; r < 32; r += 8) {
+    const int64_t n = n0 + r, k = k0 + tx;
+    if (n < N && k < Kp) out[n * Kp + k] = from_f32<T16>(tile[tx][r]);
+  }
+}
+
+}  // namespace mdc
+
+using namespace mdc;
+
+MDC_API uint64_t mgpuOpsLaunchCount(void) { return g_launch_count.load(); }
+
+MDC_API void mgpuAdd(const float *a, const float *b, float *c, int64_t n, void *stream) {
+  if (n <= 0) return;
+  const DeviceInfo &di = device_info();
+  if (!di.ok) return;
+  mdc_add_f32<<<ew_grid((n + 3) / 4, di.sms), kEwBlock, 0, as_stream(stream)>>>(a, b, c, n);
+  launched("mdc_add_f32");
+}
+
+MDC_API void mgpuBiasAdd(const float *x, const float *bias, float *y, int64_t rows, int64_t cols,
+                         void *stream) {
+  if (rows <= 0 || cols <= 0) return;
+  const DeviceInfo &di = device_info();
+  if (!di.ok) return;
+  mdc_bias_add_f32<<<ew_grid((rows * cols + 3) / 4, di.sms), kEwBlock, 0, as_stream(stream)>>>(
+      x, bias, y, rows, cols);
+  launched("mdc_bias_add_f32");
+}
+
+MDC_API void mgpuActivation(const float *x, float *y, int64_t n, int32_t act, void *stream) {
+  if (n <= 0) return;
+  const DeviceInfo &di = device_info();
+  if (!di.ok) return;
+  const int grid = ew_grid((n + 3) / 4, di.sms);
+  cudaStream_t s = as_stream(stream);
+  switch (act) {
+  case MGPU_ACT_RELU:
+    mdc_relu_f32<<<grid, kEwBlock, 0, s>>>(x, y, n);
+    break;
+  case MGPU_ACT_GELU_ERF:
+    mdc_gelu_erf_f32<<<grid, kEwBlock, 0, s>>>(x, y, n);
+    break;
+  case MGPU_ACT_GELU_TANH:
+    mdc_gelu_tanh_f32<<<grid, kEwBlock, 0, s>>>(x, y, n);
+    break;
+  case MGPU_ACT_NONE:
+    if (x != y) check_cuda(cudaMemcpyAsync(y, x, n * sizeof(float), cudaMemcpyDeviceToDevice, s), "copy");
+    return;
+  default:
+    fail("mgpuActivation: unknown activation");
+    return;
+  }
+  launched("mdc_activation");
+}
+
+MDC_API void mgpuCast(const void *src, int32_t sd, void *dst, int32_t dd, int64_t n, void *stream) {
+  if (n <= 0) return;
+  const DeviceInfo &di = device_info();
+  if (!di.ok) return;
+  cudaStream_t s = as_stream(stream);
+  const int grid = ew_grid((n + 7) / 8, di.sms);
+  if (sd == dd) {
+    if (src != dst)
+      check_cuda(cudaMemcpyAsync(dst, src, n * dtype_size(sd), cudaMemcpyDeviceToDevice, s), "copy");
+    return;
+  }
+  if (sd == MGPU_DTYPE_F32 && dd == MGPU_DTYPE_F16)
+    cast_f32_to_16<__half><<<grid, kEwBlock, 0, s>>>((const float *)src, (__half *)dst, n);
+  else if (sd == MGPU_DTYPE_F32 && dd == MGPU_DTYPE_BF16)
+    cast_f32_to_16<__nv_bfloat16><<<grid, kEwBlock, 0, s>>>((const float *)src, (__nv_bfloat16 *)dst, n);
+  else if (sd == MGPU_DTYPE_F16 && dd == MGPU_DTYPE_F32)
+    cast_16_to_f32<__half><<<grid, kEwBlock, 0, s>>>((const __half *)src, (float *)dst, n);
+  else if (sd == MGPU_DTYPE_BF16 && dd == MGPU_DTYPE_F32)
+    cast_16_to_f32<__nv_bfloat16><<<grid, kEwBlock, 0, s>>>((const __nv_bfloat16 *)src, (float *)dst, n);
+  else if (sd == MGPU_DTYPE_F16 && dd == MGPU_DTYPE_BF16)
+    cast_generic<__half, __nv_bfloat16><<<grid, kEwBlock, 0, s>>>((const __half *)src, (__nv_bfloat16 *)dst, n);
+  else if (sd == MGPU_DTYPE_BF16 && dd == MGPU_DTYPE_F16)
+    cast_generic<__nv_bfloat16, __half><<<grid, kEwBlock, 0, s>>>((const __nv_bfloat16 *)src, (__half *)dst, n);
+  else {
+    fail("mgpuCast: unknown element type");
+    return;
+  }
+  launched("mdc_cast");
+}
+
+namespace mdc {
+// fp32 [R,C] -> 16-bit [R,Cp]; plain cast when C == Cp.
+void cast_rows_padded(const float *src, void *dst, int64_t R, int64_t C, int64_t Cp, int32_t dtype,
+                      cudaStream_t s) {
+  if (C == Cp) {
+    mgpuCast(src, MGPU_DTYPE_F32, dst, dtype, R * C, s);
+    return;
+  }
+  const DeviceInfo &di = device_info();
+  if (!di.ok) return;
+  const int grid = ew_grid(R * Cp, di.sms);
+  if (dtype == MGPU_DTYPE_F16)
+    cast_pad_rows<__half><<<grid, kEwBlock, 0, s>>>(src, (__half *)dst, R, C, Cp);
+  else
+    cast_pad_rows<__nv_bfloat16><<<grid, kEwBlock, 0, s>>>(src, (__nv_bfloat16 *)dst, R, C, Cp);
+  launched("mdc_cast_pad_rows");
+}
+}  // namespace mdc
+
+MDC_API void mgpuPackWeight(const float *w, void *packed, int64_t K, int64_t N, int32_t dtype,
+                            void *stream) {
+  if (K <= 0 || N <= 0) return;
+  if (!dtype_is16(dtype)) {
+    fail("mgpuPackWeight: dtype must be F16 or BF16");
+    return;
+  }
+  if (!device_info().ok) return;
+  const int64_t Kp = (K + 7) / 8 * 8;
+  dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((Kp + 31) / 32));
+  if (dtype == MGPU_DTYPE_F16)
+    pack_weight_kernel<__half><<<grid, 256, 0, as_stream(stream)>>>(w, (__half *)packed, K, N, Kp);
+  else
+    pack_weight_kernel<__nv_bfloat16><<<grid, 256, 0, as_stream(stream)>>>(w, (__nv_bfloat16 *)packed, K, N, Kp);
+  launched("mdc_pack_weight");
+}

@@ -1,0 +1,339 @@
+// Transformer encoder layer / stack orchestration on top of the hand-written kernels.
+//
+// Replaces mgpuLLMDecodingContextLayer (lib/Kernels/GPU/LLM.cu:26-158).  The reference
+// re-casts every weight fp32->fp16 on every call, allocates about twenty temporaries per
+// call and runs cast / LayerNorm / 4 cuBLASLt Gemms / a vendored fused-MHA cubin on two
+// streams.  Here the weights are packed once into the tensor-core operand layout and kept
+// in a handle; a layer is 7 kernel launches on one stream:
+//   post-LN: qkv = Gemm(x) ; att = Attention(qkv) ; a = Gemm(att)+bias+x ; y1 = LN1(a) ;
+//            f1 = act(Gemm(y1)+b1) ; f2 = Gemm(f1)+b2+y1 ; y = LN2(f2)
+//   pre-LN : n1 = LN1(x) ; qkv = Gemm(n1) ; att ; a = Gemm(att)+bias+x ; n2 = LN2(a) ;
+//            f1 = act(Gemm(n2)+b1) ; y = Gemm(f1)+b2+a
+// Bias, activation, residual add and the output type conversion ride in the Gemm epilogue;
+// attention reads the packed QKV rows directly (no split / transpose kernel, the job of
+// lib/Kernels/GPU/Transpose.cu:6-85).  Activations between kernels are 16-bit, statistics
+// and accumulation fp32; the boundary is fp32 like the reference's.
+#include <vector>
+
+#include "ops_common.h"
+
+namespace mdc {
+
+struct LayerWeights {
+  void *wqkv = nullptr, *wo = nullptr, *w1 = nullptr, *w2 = nullptr;  // 16-bit [N, K]
+  float *bqkv = nullptr, *bo = nullptr, *b1 = nullptr, *b2 = nullptr;
+  float *ln1_g = nullptr, *ln1_b = nullptr, *ln2_g = nullptr, *ln2_b = nullptr;
+};
+
+struct Workspace {
+  int64_t tokens = 0;
+  void *cur = nullptr, *qkv = nullptr, *att = nullptr, *a = nullptr, *n1 = nullptr, *f1 = nullptr;
+};
+
+struct EncoderStack {
+  int64_t layers_n = 0, d = 0, F = 0, H = 0;
+  bool norm_first = false, causal = false;
+  int32_t act = MGPU_ACT_GELU_ERF, dtype = MGPU_DTYPE_F16;
+  float eps = 1e-5f;
+  std::vector<LayerWeights> layers;
+  Workspace ws;
+  // host-buffer pipeline state
+  cudaStream_t s_in = nullptr, s_comp = nullptr, s_out = nullptr;
+  cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_comp[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
+  void *x_dev[2] = {nullptr, nullptr}, *y_dev[2] = {nullptr, nullptr};
+  int32_t *lens_dev[2] = {nullptr, nullptr};
+  int64_t pipe_seqs = 0, pipe_seq_len = 0;
+  // stream that last used the workspace; a run on another stream first waits for it
+  void *last_stream = nullptr;
+  bool used = false;
+};
+
+// The activation workspace is shared by all runs of a stack: order a run on a new stream
+// after the previous run's stream has drained.
+static void order_after_previous(EncoderStack *st, void *stream) {
+  if (st->used && st->last_stream != stream) cudaStreamSynchronize(as_stream(st->last_stream));
+  st->last_stream = stream;
+  st->used = true;
+}
+
+static void free_ws(Workspace &w, void *stream) {
+  void **p[] = {&w.cur, &w.qkv, &w.att, &w.a, &w.n1, &w.f1};
+  for (auto q : p) {
+    if (*q) mgpuMemFreeAsync(*q, stream);
+    *q = nullptr;
+  }
+  w.tokens = 0;
+}
+
+static bool ensure_ws(EncoderStack *st, int64_t tokens, void *stream) {
+  Workspace &w = st->ws;
+  if (w.tokens >= tokens) return true;
+  free_ws(w, stream);
+  const uint64_t T = static_cast<uint64_t>(tokens), d = st->d, F = st->F;
+  w.cur = mgpuMemAllocAsync(T * d * 2, stream);
+  w.qkv = mgpuMemAllocAsync(T * 3 * d * 2, stream);
+  w.att = mgpuMemAllocAsync(T * d * 2, stream);
+  w.a = mgpuMemAllocAsync(T * d * 2, stream);
+  w.n1 = mgpuMemAllocAsync(T * d * 2, stream);
+  w.f1 = mgpuMemAllocAsync(T * F * 2, stream);
+  if (!w.cur || !w.qkv || !w.att || !w.a || !w.n1 || !w.f1) {
+    free_ws(w, stream);
+    fail("encoder stack: out of device memory for the activation workspace");
+    return false;
+  }
+  w.tokens = tokens;
+  return true;
+}
+
+static float *dup_f32(const float *src, int64_t n, void *stream) {
+  if (!src) return nullptr;
+  float *dst = static_cast<float *>(mgpuMemAllocAsync(static_cast<uint64_t>(n) * 4, stream));
+  if (dst) check_cuda(cudaMemcpyAsync(dst, src, n * 4, cudaMemcpyDeviceToDevice, as_stream(stream)), "copy bias");
+  return dst;
+}
+
+static void *pack(const float *w, int64_t K, int64_t N, int32_t dtype, void *stream) {
+  if (!w) return nullptr;
+  void *dst = mgpuMemAllocAsync(static_cast<uint64_t>(N) * K * 2, stream);
+  if (dst) mgpuPackWeight(w, dst, K, N, dtype, stream);
+  return dst;
+}
+
+static void free_layer(LayerWeights &lw, void *stream) {
+  void *p[] = {lw.wqkv, lw.wo, lw.w1, lw.w2, lw.bqkv, lw.bo, lw.b1, lw.b2, lw.ln1_g, lw.ln1_b, lw.ln2_g, lw.ln2_b};
+  for (void *q : p)
+    if (q) mgpuMemFreeAsync(q, stream);
+  lw = LayerWeights();
+}
+
+static void destroy_stack(EncoderStack *st, void *stream) {
+  if (!st) return;
+  for (auto &lw : st->layers) free_layer(lw, stream);
+  free_ws(st->ws, stream);
+  for (int i = 0; i < 2; ++i) {
+    if (st->x_dev[i]) mgpuMemFreeAsync(st->x_dev[i], stream);
+    if (st->y_dev[i]) mgpuMemFreeAsync(st->y_dev[i], stream);
+    if (st->lens_dev[i]) mgpuMemFreeAsync(st->lens_dev[i], stream);
+    if (st->ev_in[i]) cudaEventDestroy(st->ev_in[i]);
+    if (st->ev_comp[i]) cudaEventDestroy(st->ev_comp[i]);
+    if (st->ev_out[i]) cudaEventDestroy(st->ev_out[i]);
+  }
+  if (st->s_in) cudaStreamDestroy(st->s_in);
+  if (st->s_comp) cudaStreamDestroy(st->s_comp);
+  if (st->s_out) cudaStreamDestroy(st->s_out);
+  delete st;
+}
+
+// x_f32 != nullptr: input is fp32 and is cast first; else `cur` already holds 16-bit input.
+// y_f32 receives the fp32 result.
+static void run_stack(EncoderStack *st, const float *x_f32, const int32_t *seq_lens, float *y_f32,
+                      int64_t B, int64_t S, void *stream) {
+  const int64_t T = B * S, d = st->d, F = st->F;
+  const int32_t dt = st->dtype;
+  Workspace &w = st->ws;
+  mgpuCast(x_f32, MGPU_DTYPE_F32, w.cur, dt, T * d, stream);
+  const int64_t L = st->layers_n;
+  for (int64_t l = 0; l < L; ++l) {
+    const LayerWeights &lw = st->layers[l];
+    const bool last = (l + 1 == L);
+    if (!lw.wqkv || !lw.wo || !lw.w1 || !lw.w2) {
+      fail("encoder stack: layer weights were not set");
+      return;
+    }
+    if (st->norm_first) {
+      mgpuLayerNormEx(w.cur, nullptr, lw.ln1_g, lw.ln1_b, nullptr, w.n1, st->eps, T, d, dt, dt, stream);
+      mgpuMatmulEx16(w.n1, lw.wqkv, lw.bqkv, nullptr, w.qkv, T, 3 * d, d, dt, dt, MGPU_ACT_NONE, stream);
+      mgpuAttention(w.qkv, seq_lens, w.att, B, S, st->H, d / st->H, st->causal, dt, stream);
+      mgpuMatmulEx16(w.att, lw.wo, lw.bo, w.cur, w.a, T, d, d, dt, dt, MGPU_ACT_NONE, stream);
+      mgpuLayerNormEx(w.a, nullptr, lw.ln2_g, lw.ln2_b, nullptr, w.n1, st->eps, T, d, dt, dt, stream);
+      mgpuMatmulEx16(w.n1, lw.w1, lw.b1, nullptr, w.f1, T, F, d, dt, dt, st->act, stream);
+      if (last)
+        mgpuMatmulEx16(w.f1, lw.w2, lw.b2, w.a, y_f32, T, d, F, dt, MGPU_DTYPE_F32, MGPU_ACT_NONE, stream);
+      else
+        mgpuMatmulEx16(w.f1, lw.w2, lw.b2, w.a, w.cur, T, d, F, dt, dt, MGPU_ACT_NONE, stream);
+    } else {
+      mgpuMatmulEx16(w.cur, lw.wqkv, lw.bqkv, nullptr, w.qkv, T, 3 * d, d, dt, dt, MGPU_ACT_NONE, stream);
+      mgpuAttention(w.qkv, seq_lens, w.att, B, S, st->H, d / st->H, st->causal, dt, stream);
+      mgpuMatmulEx16(w.att, lw.wo, lw.bo, w.cur, w.a, T, d, d, dt, dt, MGPU_ACT_NONE, stream);
+      mgpuLayerNormEx(w.a, nullptr, lw.ln1_g, lw.ln1_b, nullptr, w.n1, st->eps, T, d, dt, dt, stream);
+      mgpuMatmulEx16(w.n1, lw.w1, lw.b1, nullptr, w.f1, T, F, d, dt, dt, st->act, stream);
+      mgpuMatmulEx16(w.f1, lw.w2, lw.b2, w.n1, w.a, T, d, F, dt, dt, MGPU_ACT_NONE, stream);
+      if (last)
+        mgpuLayerNormEx(w.a, nullptr, lw.ln2_g, lw.ln2_b, nullptr, y_f32, st->eps, T, d, dt, MGPU_DTYPE_F32, stream);
+      else
+        mgpuLayerNormEx(w.a, nullptr, lw.ln2_g, lw.ln2_b, nullptr, w.cur, st->eps, T, d, dt, dt, stream);
+    }
+  }
+}
+
+static bool valid_config(int64_t L, int64_t d, int64_t F, int64_t H, int32_t act, int32_t dtype) {
+  if (L <= 0 || d <= 0 || F <= 0 || H <= 0) { fail("encoder: sizes must be positive"); return false; }
+  if (d % H != 0 || d / H != 64) { fail("encoder: d_model / head_num must be 64"); return false; }
+  if (d % 8 || F % 8) { fail("encoder: d_model and feed_forward_dim must be multiples of 8"); return false; }
+  if (!dtype_is16(dtype)) { fail("encoder: dtype must be F16 or BF16"); return false; }
+  if (act < MGPU_ACT_NONE || act > MGPU_ACT_GELU_TANH) { fail("encoder: unknown activation"); return false; }
+  return true;
+}
+
+}  // namespace mdc
+
+using namespace mdc;
+
+MDC_API void *mgpuEncoderStackCreate(int64_t num_layers, int64_t d_model, int64_t feed_forward_dim,
+                                     int64_t head_num, bool norm_first, bool causal, int32_t act,
+                                     int32_t dtype, float eps) {
+  if (!device_info().ok) return nullptr;
+  if (!valid_config(num_layers, d_model, feed_forward_dim, head_num, act, dtype)) return nullptr;
+  EncoderStack *st = new EncoderStack();
+  st->layers_n = num_layers;
+  st->d = d_model;
+  st->F = feed_forward_dim;
+  st->H = head_num;
+  st->norm_first = norm_first;
+  st->causal = causal;
+  st->act = act;
+  st->dtype = dtype;
+  st->eps = eps;
+  st->layers.resize(static_cast<size_t>(num_layers));
+  return st;
+}
+
+MDC_API void mgpuEncoderStackSetLayer(void *stack, int64_t layer, const float *qkv_weight,
+                                      const float *qkv_bias, const float *proj_weight,
+                                      const float *proj_bias, const float *ffn1_weight,
+                                      const float *ffn1_bias, const float *ffn2_weight,
+                                      const float *ffn2_bias, const float *ln1_gamma,
+                                      const float *ln1_beta, const float *ln2_gamma,
+                                      const float *ln2_beta, void *stream) {
+  EncoderStack *st = static_cast<EncoderStack *>(stack);
+  if (!st || layer < 0 || layer >= st->layers_n) { fail("mgpuEncoderStackSetLayer: bad handle or layer index"); return; }
+  if (!qkv_weight || !proj_weight || !ffn1_weight || !ffn2_weight) { fail("mgpuEncoderStackSetLayer: weight matrices are required"); return; }
+  LayerWeights &lw = st->layers[static_cast<size_t>(layer)];
+  free_layer(lw, stream);
+  const int64_t d = st->d, F = st->F;
+  lw.wqkv = pack(qkv_weight, d, 3 * d, st->dtype, stream);
+  lw.wo = pack(proj_weight, d, d, st->dtype, stream);
+  lw.w1 = pack(ffn1_weight, d, F, st->dtype, stream);
+  lw.w2 = pack(ffn2_weight, F, d, st->dtype, stream);
+  lw.bqkv = dup_f32(qkv_bias, 3 * d, stream);
+  lw.bo = dup_f32(proj_bias, d, stream);
+  lw.b1 = dup_f32(ffn1_bias, F, stream);
+  lw.b2 = dup_f32(ffn2_bias, d, stream);
+  lw.ln1_g = dup_f32(ln1_gamma, d, stream);
+  lw.ln1_b = dup_f32(ln1_beta, d, stream);
+  lw.ln2_g = dup_f32(ln2_gamma, d, stream);
+  lw.ln2_b = dup_f32(ln2_beta, d, stream);
+}
+
+MDC_API void mgpuEncoderStackRun(void *stack, const float *x, const int32_t *seq_lens, float *y,
+                                 int64_t batch, int64_t seq_len, void *stream) {
+  EncoderStack *st = static_cast<EncoderStack *>(stack);
+  if (!st) { fail("mgpuEncoderStackRun: null handle"); return; }
+  if (batch <= 0 || seq_len <= 0) return;
+  order_after_previous(st, stream);
+  if (!ensure_ws(st, batch * seq_len, stream)) return;
+  run_stack(st, x, seq_lens, y, batch, seq_len, stream);
+}
+
+MDC_API void mgpuEncoderStackDestroy(void *stack) {
+  EncoderStack *st = static_cast<EncoderStack *>(stack);
+  if (!st) return;
+  // blocks go back to the pool ordered after everything already queued on the device
+  cudaDeviceSynchronize();
+  destroy_stack(st, nullptr);
+}
+
+MDC_API void mgpuEncoderStackRunHost(void *stack, const float *x_host, const int32_t *seq_lens_host,
+                                     float *y_host, int64_t batch, int64_t seq_len, int32_t chunks) {
+  EncoderStack *st = static_cast<EncoderStack *>(stack);
+  if (!st) { fail("mgpuEncoderStackRunHost: null handle"); return; }
+  if (batch <= 0 || seq_len <= 0) return;
+  if (chunks < 1) chunks = 1;
+  if (chunks > batch) chunks = static_cast<int32_t>(batch);
+  const int64_t per = (batch + chunks - 1) / chunks;
+  const int64_t d = st->d;
+  if (!st->s_in) {
+    bool ok = check_cuda(cudaStreamCreateWithFlags(&st->s_in, cudaStreamNonBlocking), "stream") &&
+              check_cuda(cudaStreamCreateWithFlags(&st->s_comp, cudaStreamNonBlocking), "stream") &&
+              check_cuda(cudaStreamCreateWithFlags(&st->s_out, cudaStreamNonBlocking), "stream");
+    for (int i = 0; ok && i < 2; ++i)
+      ok = check_cuda(cudaEventCreateWithFlags(&st->ev_in[i], cudaEventDisableTiming), "event") &&
+           check_cuda(cudaEventCreateWithFlags(&st->ev_comp[i], cudaEventDisableTiming), "event") &&
+           check_cuda(cudaEventCreateWithFlags(&st->ev_out[i], cudaEventDisableTiming), "event");
+    if (!ok) return;
+  }
+  if (st->pipe_seqs < per || st->pipe_seq_len < seq_len) {
+    for (int i = 0; i < 2; ++i) {
+      if (st->x_dev[i]) mgpuMemFreeAsync(st->x_dev[i], st->s_comp);
+      if (st->y_dev[i]) mgpuMemFreeAsync(st->y_dev[i], st->s_comp);
+      if (st->lens_dev[i]) mgpuMemFreeAsync(st->lens_dev[i], st->s_comp);
+      const uint64_t bytes = static_cast<uint64_t>(per) * seq_len * d * 4;
+      st->x_dev[i] = mgpuMemAllocAsync(bytes, st->s_comp);
+      st->y_dev[i] = mgpuMemAllocAsync(bytes, st->s_comp);
+      st->lens_dev[i] = static_cast<int32_t *>(mgpuMemAllocAsync(static_cast<uint64_t>(per) * 4, st->s_comp));
+      if (!st->x_dev[i] || !st->y_dev[i] || !st->lens_dev[i]) { fail("encoder stack: out of device memory for the IO buffers"); return; }
+    }
+    st->pipe_seqs = per;
+    st->pipe_seq_len = seq_len;
+    check_cuda(cudaStreamSynchronize(st->s_comp), "sync");
+  }
+  order_after_previous(st, st->s_comp);
+  if (!ensure_ws(st, per * seq_len, st->s_comp)) return;
+  int n = 0;
+  for (int64_t b0 = 0; b0 < batch; b0 += per, ++n) {
+    const int set = n & 1;
+    const int64_t nb = (batch - b0 < per) ? batch - b0 : per;
+    const size_t elems = static_cast<size_t>(nb) * seq_len * d;
+    const size_t off = static_cast<size_t>(b0) * seq_len * d;
+    if (n >= 2) cudaStreamWaitEvent(st->s_in, st->ev_comp[set], 0);  // x_dev[set] consumed
+    check_cuda(cudaMemcpyAsync(st->x_dev[set], x_host + off, elems * 4, cudaMemcpyHostToDevice, st->s_in), "H2D");
+    if (seq_lens_host)
+      check_cuda(cudaMemcpyAsync(st->lens_dev[set], seq_lens_host + b0, nb * 4, cudaMemcpyHostToDevice, st->s_in), "H2D lens");
+    cudaEventRecord(st->ev_in[set], st->s_in);
+    cudaStreamWaitEvent(st->s_comp, st->ev_in[set], 0);
+    if (n >= 2) cudaStreamWaitEvent(st->s_comp, st->ev_out[set], 0);  // y_dev[set] drained
+    run_stack(st, static_cast<const float *>(st->x_dev[set]), seq_lens_host ? st->lens_dev[set] : nullptr,
+              static_cast<float *>(st->y_dev[set]), nb, seq_len, st->s_comp);
+    cudaEventRecord(st->ev_comp[set], st->s_comp);
+    cudaStreamWaitEvent(st->s_out, st->ev_comp[set], 0);
+    check_cuda(cudaMemcpyAsync(y_host + off, st->y_dev[set], elems * 4, cudaMemcpyDeviceToHost, st->s_out), "D2H");
+    cudaEventRecord(st->ev_out[set], st->s_out);
+  }
+  check_cuda(cudaStreamSynchronize(st->s_out), "sync");
+  check_cuda(cudaStreamSynchronize(st->s_comp), "sync");
+  check_cuda(cudaStreamSynchronize(st->s_in), "sync");
+}
+
+MDC_API void mgpuTransformerEncoderLayer(const float *input, const float *qkv_weight, const float *qkv_bias,
+                                         const float *proj_weight, const float *proj_bias,
+                                         const float *ffn1_weight, const float *ffn1_bias,
+                                         const float *ffn2_weight, const float *ffn2_bias,
+                                         const float *ln1_gamma, const float *ln1_beta,
+                                         const float *ln2_gamma, const float *ln2_beta,
+                                         const int32_t *seq_lens, float *output, int64_t batch,
+                                         int64_t seq_len, int64_t d_model, int64_t feed_forward_dim,
+                                         int64_t head_num, bool norm_first, bool causal, int32_t act,
+                                         int32_t dtype, float eps, void *stream) {
+  if (batch <= 0 || seq_len <= 0) return;
+  EncoderStack *st = static_cast<EncoderStack *>(
+      mgpuEncoderStackCreate(1, d_model, feed_forward_dim, head_num, norm_first, causal, act, dtype, eps));
+  if (!st) return;
+  mgpuEncoderStackSetLayer(st, 0, qkv_weight, qkv_bias, proj_weight, proj_bias, ffn1_weight, ffn1_bias,
+                           ffn2_weight, ffn2_bias, ln1_gamma, ln1_beta, ln2_gamma, ln2_beta, stream);
+  if (ensure_ws(st, batch * seq_len, stream)) run_stack(st, input, seq_lens, output, batch, seq_len, stream);
+  // everything the layer used goes back to the pool in stream order, as the reference does
+  // with its mgpuMemFreeAsync calls (LLM.cu:143-154)
+  destroy_stack(st, stream);
+}
+
+// Legacy entry point: LayerNorm without affine, no QKV bias, full-length sequences, fp16.
+MDC_API void mgpuLLMDecodingContextLayer(float *input, float *qkv, float *gemm_weight, float *gemm_bias,
+                                         float *ffn1_weight, float *ffn1_bias, float *ffn2_weight,
+                                         float *ffn2_bias, float *output, int64_t batch, int64_t seq_len,
+                                         int64_t d_model, int64_t feed_forward_dim, int64_t head_num,
+                                         bool norm_first, bool is_casual, bool is_relu, void *stream) {
+  mgpuTransformerEncoderLayer(input, qkv, nullptr, gemm_weight, gemm_bias, ffn1_weight, ffn1_bias,
+                              ffn2_weight, ffn2_bias, nullptr, nullptr, nullptr, nullptr, nullptr, output,
+                              batch, seq_len, d_model, feed_forward_dim, head_num, norm_first, is_casual,
+                              is_relu ? MGPU_ACT_RELU : MGPU_ACT_GELU_ERF, MGPU_DTYPE_F16, 1e-5f, stream);
+}

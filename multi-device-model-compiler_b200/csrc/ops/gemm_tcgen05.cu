@@ -1,0 +1,419 @@
+// Tensor-core Gemm for sm_100a: out[M,N] = act(A[M,K] . W[N,K]^T + bias[N]) + residual[M,N]
+// with 16-bit operands (fp16 or bf16), fp32 accumulation in tensor memory and a fused
+// epilogue.  Replaces the cuBLASLt calls of lib/Kernels/GPU/Ops.cu:59-120 (mgpuMatmul) and
+// :136-234 (mgpuMatmulEx: bias / ReLU / residual epilogues).
+//
+// Structure (one persistent CTA per SM, 10 warps):
+//   warp 0   TMA producer: cp.async.bulk.tensor tiles of A (128 x 64) and W (256 x 64) into
+//            a 4-stage ring of 128-byte-swizzled shared memory, completion on mbarriers.
+//   warp 1   MMA issuer: one thread issues tcgen05.mma (M=128, N=256, K=16) reading the
+//            shared-memory tiles through matrix descriptors; tcgen05.commit releases the
+//            stage to the producer and, after the last k-block, hands the accumulator over.
+//   warps 2-9 epilogue: tcgen05.ld the 128 x 256 fp32 accumulator out of TMEM (each warp
+//            its 32-lane quarter, two warps per quarter splitting the columns), add bias,
+//            apply the activation, add the residual, convert and store.
+// TMEM holds two accumulators (2 x 256 columns) so the epilogue of tile i overlaps the
+// mainloop of tile i+1.  No cluster launch and no multicast: every CTA fetches its own tiles
+// and relies on L2 for reuse.  All waits are bounded (see ptx_sm100.cuh).
+#include <type_traits>
+
+#include "activation.cuh"
+#include "ops_common.h"
+#include "ptx_sm100.cuh"
+
+namespace mdc {
+
+namespace gemm {
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + EPI_WARPS * 32;
+constexpr int TMEM_COLS = 512;
+constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024;  // + alignment slack
+}  // namespace gemm
+
+struct GemmParams {
+  int M, N, K;  // K already padded to a multiple of 8
+  const float *bias;
+  const void *residual;
+  void *out;
+  int out_vec_ok;   // rows of out / residual can be accessed with 16-byte vectors
+  int bias_vec_ok;  // bias is 16-byte aligned
+  int num_m_blocks, num_n_blocks;
+  uint32_t *err;
+};
+
+template <typename TOut>
+__device__ __forceinline__ void store_out8(TOut *dst, const float *v);
+template <>
+__device__ __forceinline__ void store_out8<float>(float *dst, const float *v) {
+  reinterpret_cast<float4 *>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4 *>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store_out8<__half>(__half *dst, const float *v) {
+  uint4 o;
+  *reinterpret_cast<__half2 *>(&o.x) = __floats2half2_rn(v[0], v[1]);
+  *reinterpret_cast<__half2 *>(&o.y) = __floats2half2_rn(v[2], v[3]);
+  *reinterpret_cast<__half2 *>(&o.z) = __floats2half2_rn(v[4], v[5]);
+  *reinterpret_cast<__half2 *>(&o.w) = __floats2half2_rn(v[6], v[7]);
+  *reinterpret_cast<uint4 *>(dst) = o;
+}
+template <>
+__device__ __forceinline__ void store_out8<__nv_bfloat16>(__nv_bfloat16 *dst, const float *v) {
+  uint4 o;
+  *reinterpret_cast<__nv_bfloat162 *>(&o.x) = __floats2bfloat162_rn(v[0], v[1]);
+  *reinterpret_cast<__nv_bfloat162 *>(&o.y) = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<__nv_bfloat162 *>(&o.z) = __floats2bfloat162_rn(v[4], v[5]);
+  *reinterpret_cast<__nv_bfloat162 *>(&o.w) = __floats2bfloat162_rn(v[6], v[7]);
+  *reinterpret_cast<uint4 *>(dst) = o;
+}
+__device__ __forceinline__ void load_res8(const __half *src, float *v) {
+  const uint4 r = *reinterpret_cast<const uint4 *>(src);
+  const __half2 *h = reinterpret_cast<const __half2 *>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(h[i]);
+    v[2 * i] = f.x; v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void load_res8(const __nv_bfloat16 *src, float *v) {
+  const uint4 r = *reinterpret_cast<const uint4 *>(src);
+  const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x; v[2 * i + 1] = f.y;
+  }
+}
+
+template <typename T16, typename TOut, int ACT>
+__global__ void __launch_bounds__(gemm::THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  using namespace gemm;
+  using namespace ptx;
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ uint32_t abort_flag_s;
+  volatile uint32_t *abort_flag = &abort_flag_s;
+
+  // 128-byte-swizzled tiles need 1024-byte aligned bases
+  uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag_s = 0;
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full_bar[a], 1);
+      mbar_init(&acc_empty_bar[a], EPI_WARPS * 32);
+    }
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        const int m_blk = tile % p.num_m_blocks, n_blk = tile / p.num_m_blocks;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            atomicCAS(p.err, 0u, 0x10000000u | static_cast<uint32_t>(stage));
+            ok = false;
+            break;
+          }
+          uint8_t *sa = tiles + stage * STAGE_BYTES;
+          uint8_t *sb = sa + A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m_blk * BM);
+          tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n_blk * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc =
+          make_idesc_f16(BM, BN, sizeof(T16) == 2 && std::is_same<T16, __nv_bfloat16>::value, false, false);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
+          atomicCAS(p.err, 0u, 0x30000000u | static_cast<uint32_t>(acc));
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            atomicCAS(p.err, 0u, 0x20000000u | static_cast<uint32_t>(stage));
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
+          const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t b_desc = make_smem_desc_sw128(sa + A_BYTES, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // 16 k-elements = 32 bytes further along the 128-byte swizzled row
+            umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * k),
+                        b_desc + static_cast<uint64_t>(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full_bar[acc]);  // accumulator complete
+        if ((acc ^= 1) == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;   // TMEM lane quarter this warp may access
+    const int half_sel = ew >> 2;   // which 128 accumulator columns this warp handles
+    TOut *out = static_cast<TOut *>(p.out);
+    const T16 *res = static_cast<const T16 *>(p.residual);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int m_blk = tile % p.num_m_blocks, n_blk = tile / p.num_m_blocks;
+      if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag)) {
+        atomicCAS(p.err, 0u, 0x40000000u | static_cast<uint32_t>(acc));
+        break;
+      }
+      tc_fence_after();
+      const int row = m_blk * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 2 / 32; ++chunk) {
+        const int col0 = half_sel * (BN / 2) + chunk * 32;
+        const int gcol0 = n_blk * BN + col0;
+        if (gcol0 >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + static_cast<uint32_t>(acc * BN + col0) +
+                          (static_cast<uint32_t>(quarter * 32) << 16),
+                      r);
+        tmem_ld_wait();
+        const int ncols = min(32, p.N - gcol0);
+        if (ncols == 32 && p.out_vec_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[8 * g + j]);
+            if (p.bias) {
+              if (p.bias_vec_ok) {
+                const float4 b0 = __ldg(reinterpret_cast<const float4 *>(p.bias + gcol0 + 8 * g));
+                const float4 b1 = __ldg(reinterpret_cast<const float4 *>(p.bias + gcol0 + 8 * g) + 1);
+                v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+              } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += __ldg(p.bias + gcol0 + 8 * g + j);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = act_apply_t<ACT>(v[j]);
+            if (row_ok) {
+              const size_t off = static_cast<size_t>(row) * p.N + gcol0 + 8 * g;
+              if (res) {
+                float rv[8];
+                load_res8(res + off, rv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += rv[j];
+              }
+              store_out8<TOut>(out + off, v);
+            }
+          }
+        } else if (row_ok) {
+          // ragged edge or unaligned rows: one element at a time (static register indices)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (j < ncols) {
+              float v = __uint_as_float(r[j]);
+              if (p.bias) v += __ldg(p.bias + gcol0 + j);
+              v = act_apply_t<ACT>(v);
+              const size_t off = static_cast<size_t>(row) * p.N + gcol0 + j;
+              if (res) v += static_cast<float>(res[off]);
+              out[off] = static_cast<TOut>(v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty_bar[acc]);
+      if ((acc ^= 1) == 0) acc_phase ^= 1;
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------
+  if (*abort_flag) {
+    // a wait gave up: give copies still in flight time to land before the CTA retires
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) {
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------
+static uint32_t *g_err_slot = nullptr;
+
+uint32_t *device_error_slot() {
+  if (!g_err_slot) {
+    if (!check_cuda(cudaMalloc(&g_err_slot, sizeof(uint32_t)), "cudaMalloc(error slot)")) return nullptr;
+    check_cuda(cudaMemset(g_err_slot, 0, sizeof(uint32_t)), "cudaMemset(error slot)");
+  }
+  return g_err_slot;
+}
+
+bool encode_tmap_2d(CUtensorMap *map, const void *base, int32_t dtype, uint64_t inner, uint64_t outer,
+                    uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  const uint64_t gdim[2] = {inner, outer};
+  const uint64_t gstr[1] = {row_stride_bytes};
+  const uint32_t box[2] = {box_inner, box_outer};
+  const uint32_t estr[2] = {1, 1};
+  const int before = mgpuGetLastError();
+  mgpuTensorMapEncodeTiled(map,
+                           dtype == MGPU_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                    : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                           2, const_cast<void *>(base), gdim, gstr, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return before != 0 || mgpuGetLastError() == 0;
+}
+
+template <typename T16, typename TOut, int ACT>
+static void launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int grid,
+                        cudaStream_t s) {
+  auto kern = gemm_tcgen05_kernel<T16, TOut, ACT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (!check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(gemm::SMEM_BYTES)),
+                    "cudaFuncSetAttribute(gemm)"))
+      return;
+    attr_set = true;
+  }
+  kern<<<grid, gemm::THREADS, gemm::SMEM_BYTES, s>>>(ta, tb, p);
+  launched("gemm_tcgen05_kernel");
+}
+
+template <typename T16, typename TOut>
+static void launch_gemm_act(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p,
+                            int grid, int act, cudaStream_t s) {
+  switch (act) {
+  case MGPU_ACT_NONE: launch_gemm<T16, TOut, kActNone>(ta, tb, p, grid, s); break;
+  case MGPU_ACT_RELU: launch_gemm<T16, TOut, kActRelu>(ta, tb, p, grid, s); break;
+  case MGPU_ACT_GELU_ERF: launch_gemm<T16, TOut, kActGeluErf>(ta, tb, p, grid, s); break;
+  case MGPU_ACT_GELU_TANH: launch_gemm<T16, TOut, kActGeluTanh>(ta, tb, p, grid, s); break;
+  default: fail("mgpuMatmulEx16: unknown activation");
+  }
+}
+
+}  // namespace mdc
+
+using namespace mdc;
+
+MDC_API void mgpuMatmulEx16(const void *a, const void *w_nk, const float *bias, const void *residual,
+                            void *out, int64_t M, int64_t N, int64_t Kp, int32_t dtype,
+                            int32_t out_dtype, int32_t act, void *stream) {
+  if (M <= 0 || N <= 0) return;
+  const DeviceInfo &di = device_info();
+  if (!di.ok) return;
+  if (!dtype_is16(dtype)) { fail("mgpuMatmulEx16: dtype must be F16 or BF16"); return; }
+  if (Kp <= 0 || (Kp & 7)) { fail("mgpuMatmulEx16: K must be a positive multiple of 8"); return; }
+  if (M > 0x7fffffff || N > 0x7fffffff || Kp > 0x7fffffff) { fail("mgpuMatmulEx16: shape too large"); return; }
+  if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(w_nk) & 15u)) {
+    fail("mgpuMatmulEx16: operands must be 16-byte aligned");
+    return;
+  }
+  uint32_t *err = device_error_slot();
+  if (!err) return;
+
+  CUtensorMap ta, tb;
+  if (!encode_tmap_2d(&ta, a, dtype, static_cast<uint64_t>(Kp), static_cast<uint64_t>(M),
+                      static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BM) ||
+      !encode_tmap_2d(&tb, w_nk, dtype, static_cast<uint64_t>(Kp), static_cast<uint64_t>(N),
+                      static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BN))
+    return;
+
+  GemmParams p;
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(Kp);
+  p.bias = bias;
+  p.residual = residual;
+  p.out = out;
+  const size_t out_elem = dtype_size(out_dtype);
+  const int out_vec = static_cast<int>(16 / out_elem);
+  p.out_vec_ok = (N % out_vec == 0) && (N % 8 == 0) && !(reinterpret_cast<uintptr_t>(out) & 15u) &&
+                 (!residual || !(reinterpret_cast<uintptr_t>(residual) & 15u));
+  p.bias_vec_ok = bias && !(reinterpret_cast<uintptr_t>(bias) & 15u);
+  p.num_m_blocks = static_cast<int>((M + gemm::BM - 1) / gemm::BM);
+  p.num_n_blocks = static_cast<int>((N + gemm::BN - 1) / gemm::BN);
+  p.err = err;
+  const int64_t tiles = static_cast<int64_t>(p.num_m_blocks) * p.num_n_blocks;
+  if (tiles > 0x7fffffff) { fail("mgpuMatmulEx16: too many tiles"); return; }
+  const int grid = static_cast<int>(tiles < di.sms ? tiles : di.sms);
+  cudaStream_t s = as_stream(stream);
+
+  if (dtype == MGPU_DTYPE_F16) {
+    if (out_dtype == MGPU_DTYPE_F16) launch_gemm_act<__half, __half>(ta, tb, p, grid, act, s);
+    else if (out_dtype == MGPU_DTYPE_F32) launch_gemm_act<__half, float>(ta, tb, p, grid, act, s);
+    else fail("mgpuMatmulEx16: output type must be the operand type or F32");
+  } else {
+    if (out_dtype == MGPU_DTYPE_BF16) launch_gemm_act<__nv_bfloat16, __nv_bfloat16>(ta, tb, p, grid, act, s);
+    else if (out_dtype == MGPU_DTYPE_F32) launch_gemm_act<__nv_bfloat16, float>(ta, tb, p, grid, act, s);
+    else fail("mgpuMatmulEx16: output type must be the operand type or F32");
+  }
+}
+
+MDC_API uint32_t mgpuOpsCheckDeviceStatus(void *stream) {
+  uint32_t *err = device_error_slot();
+  if (!err) return 0xffffffffu;
+  uint32_t h = 0;
+  if (!check_cuda(cudaMemcpyAsync(&h, err, sizeof(h), cudaMemcpyDeviceToHost, as_stream(stream)), "read device status"))
+    return 0xffffffffu;
+  if (!check_cuda(cudaStreamSynchronize(as_stream(stream)), "cudaStreamSynchronize")) return 0xffffffffu;
+  if (h != 0) {
+    char msg[96];
+    snprintf(msg, sizeof(msg), "a tensor-core kernel gave up waiting (code 0x%08x)", h);
+    fail(msg);
+    cudaMemsetAsync(err, 0, sizeof(uint32_t), as_stream(stream));
+  }
+  return h;
+}

@@ -1,0 +1,338 @@
+// Row LayerNorm (optionally fused with a residual add) for fp32 / fp16 / bf16 tensors.
+//
+// Replaces generalAddBiasResidualLayerNormOpt2 (lib/Kernels/GPU/LayerNorm.cu:138-260),
+// which keeps one block per row, stages the row in shared memory as half2 and derives the
+// variance from E[x^2] - mean^2.  Here one WARP owns a row: the row is read from HBM once
+// with 128-bit loads straight into registers, every lane forms a Welford (count, mean, M2)
+// triple over its own elements, the 32 triples are merged with Chan's formula through
+// warp shuffles, and the normalised row is written with 128-bit stores.  No shared memory,
+// no block barrier, exactly one HBM read and one HBM write per element: the kernel is
+// bound by HBM bandwidth (8 bytes per element for fp32 in/out).
+#include "ops_common.h"
+
+namespace mdc {
+
+template <typename T>
+struct LnTraits;
+template <>
+struct LnTraits<float> {
+  static constexpr int EPC = 4;  // elements per 16-byte chunk
+  __device__ static void unpack(const uint4 &r, float *v) {
+    v[0] = __uint_as_float(r.x); v[1] = __uint_as_float(r.y);
+    v[2] = __uint_as_float(r.z); v[3] = __uint_as_float(r.w);
+  }
+  __device__ static float round(float v) { return v; }
+};
+template <>
+struct LnTraits<__half> {
+  static constexpr int EPC = 8;
+  __device__ static void unpack(const uint4 &r, float *v) {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  }
+  __device__ static float round(float v) { return __half2float(__float2half_rn(v)); }
+};
+template <>
+struct LnTraits<__nv_bfloat16> {
+  static constexpr int EPC = 8;
+  __device__ static void unpack(const uint4 &r, float *v) {
+    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  }
+  __device__ static float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
+// Stores N consecutive floats as T starting at dst (dst aligned to N * sizeof(T) bytes).
+template <typename T, int N>
+__device__ __forceinline__ void store_vec(T *dst, const float *v);
+template <>
+__device__ __forceinline__ void store_vec<float, 4>(float *dst, const float *v) {
+  __stcs(reinterpret_cast<float4 *>(dst), make_float4(v[0], v[1], v[2], v[3]));
+}
+template <>
+__device__ __forceinline__ void store_vec<float, 8>(float *dst, const float *v) {
+  __stcs(reinterpret_cast<float4 *>(dst), make_float4(v[0], v[1], v[2], v[3]));
+  __stcs(reinterpret_cast<float4 *>(dst) + 1, make_float4(v[4], v[5], v[6], v[7]));
+}
+template <>
+__device__ __forceinline__ void store_vec<__half, 4>(__half *dst, const float *v) {
+  uint2 o;
+  *reinterpret_cast<__half2 *>(&o.x) = __floats2half2_rn(v[0], v[1]);
+  *reinterpret_cast<__half2 *>(&o.y) = __floats2half2_rn(v[2], v[3]);
+  *reinterpret_cast<uint2 *>(dst) = o;
+}
+template <>
+__device__ __forceinline__ void store_vec<__half, 8>(__half *dst, const float *v) {
+  uint4 o;
+  *reinterpret_cast<__half2 *>(&o.x) = __floats2half2_rn(v[0], v[1]);
+  *reinterpret_cast<__half2 *>(&o.y) = __floats2half2_rn(v[2], v[3]);
+  *reinterpret_cast<__half2 *>(&o.z) = __floats2half2_rn(v[4], v[5]);
+  *reinterpret_cast<__half2 *>(&o.w) = __floats2half2_rn(v[6], v[7]);
+  *reinterpret_cast<uint4 *>(dst) = o;
+}
+template <>
+__device__ __forceinline__ void store_vec<__nv_bfloat16, 4>(__nv_bfloat16 *dst, const float *v) {
+  uint2 o;
+  *reinterpret_cast<__nv_bfloat162 *>(&o.x) = __floats2bfloat162_rn(v[0], v[1]);
+  *reinterpret_cast<__nv_bfloat162 *>(&o.y) = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2 *>(dst) = o;
+}
+template <>
+__device__ __forceinline__ void store_vec<__nv_bfloat16, 8>(__nv_bfloat16 *dst, const float *v) {
+  uint4 o;
+  *reinterpret_cast<__nv_bfloat162 *>(&o.x) = __floats2bfloat162_rn(v[0], v[1]);
+  *reinterpret_cast<__nv_bfloat162 *>(&o.y) = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<__nv_bfloat162 *>(&o.z) = __floats2bfloat162_rn(v[4], v[5]);
+  *reinterpret_cast<__nv_bfloat162 *>(&o.w) = __floats2bfloat162_rn(v[6], v[7]);
+  *reinterpret_cast<uint4 *>(dst) = o;
+}
+
+constexpr int kLnWarpsPerBlock = 4;
+
+// One warp per row.  n must be a multiple of EPC, rows 16-byte aligned, and
+// n <= 32 * MAXI * EPC.  Lane l owns chunks l, l+32, ... (coalesced 512-byte warp accesses).
+template <typename TIn, typename TOut, int MAXI>
+__global__ void __launch_bounds__(kLnWarpsPerBlock * 32)
+layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residual,
+                      const float *__restrict__ gamma, const float *__restrict__ beta,
+                      TIn *__restrict__ sum_out, TOut *__restrict__ y, float eps, int64_t m, int n) {
+  constexpr int EPC = LnTraits<TIn>::EPC;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarpsPerBlock + (threadIdx.x >> 5);
+  if (row >= m) return;
+  const int nchunks = n / EPC;
+  const uint4 *xr = reinterpret_cast<const uint4 *>(x + row * n);
+  const uint4 *rr = residual ? reinterpret_cast<const uint4 *>(residual + row * n) : nullptr;
+
+  float v[MAXI][EPC];
+  uint4 raw[MAXI];
+#pragma unroll
+  for (int i = 0; i < MAXI; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nchunks) raw[i] = __ldcs(xr + c);
+  }
+#pragma unroll
+  for (int i = 0; i < MAXI; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nchunks) LnTraits<TIn>::unpack(raw[i], v[i]);
+  }
+  if (rr) {
+#pragma unroll
+    for (int i = 0; i < MAXI; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nchunks) {
+        float r[EPC];
+        LnTraits<TIn>::unpack(__ldcs(rr + c), r);
+#pragma unroll
+        for (int e = 0; e < EPC; ++e) v[i][e] = LnTraits<TIn>::round(v[i][e] + r[e]);
+        if (sum_out) store_vec<TIn, EPC>(sum_out + row * n + static_cast<int64_t>(c) * EPC, v[i]);
+      }
+    }
+  }
+
+  // per-lane Welford triple (count, mean, M2) over the lane's own elements
+  float cnt = 0.f, mean = 0.f, m2 = 0.f;
+  {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXI; ++i)
+      if (lane + 32 * i < nchunks) {
+#pragma unroll
+        for (int e = 0; e < EPC; ++e) s += v[i][e];
+        cnt += static_cast<float>(EPC);
+      }
+    mean = cnt > 0.f ? s / cnt : 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXI; ++i)
+      if (lane + 32 * i < nchunks) {
+#pragma unroll
+        for (int e = 0; e < EPC; ++e) {
+          const float d = v[i][e] - mean;
+          m2 = fmaf(d, d, m2);
+        }
+      }
+  }
+  // Chan's merge of two Welford triples, butterfly over the warp
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float cnt_o = __shfl_xor_sync(0xffffffffu, cnt, off);
+    const float mean_o = __shfl_xor_sync(0xffffffffu, mean, off);
+    const float m2_o = __shfl_xor_sync(0xffffffffu, m2, off);
+    const float tot = cnt + cnt_o;
+    if (tot > 0.f) {
+      const float delta = mean_o - mean;
+      const float w = cnt_o / tot;
+      mean = fmaf(delta, w, mean);
+      m2 = m2 + m2_o + delta * delta * cnt * w;
+    }
+    cnt = tot;
+  }
+  // the two sides of a merge round differently in the last bit: take lane 0's result
+  mean = __shfl_sync(0xffffffffu, mean, 0);
+  m2 = __shfl_sync(0xffffffffu, m2, 0);
+  const float rstd = rsqrtf(m2 / static_cast<float>(n) + eps);
+
+#pragma unroll
+  for (int i = 0; i < MAXI; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nchunks) {
+      float o[EPC];
+#pragma unroll
+      for (int e4 = 0; e4 < EPC / 4; ++e4) {
+        float4 g = make_float4(1.f, 1.f, 1.f, 1.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (gamma) g = __ldg(reinterpret_cast<const float4 *>(gamma) + c * (EPC / 4) + e4);
+        if (beta) b = __ldg(reinterpret_cast<const float4 *>(beta) + c * (EPC / 4) + e4);
+        o[4 * e4 + 0] = fmaf((v[i][4 * e4 + 0] - mean) * rstd, g.x, b.x);
+        o[4 * e4 + 1] = fmaf((v[i][4 * e4 + 1] - mean) * rstd, g.y, b.y);
+        o[4 * e4 + 2] = fmaf((v[i][4 * e4 + 2] - mean) * rstd, g.z, b.z);
+        o[4 * e4 + 3] = fmaf((v[i][4 * e4 + 3] - mean) * rstd, g.w, b.w);
+      }
+      store_vec<TOut, EPC>(y + row * n + static_cast<int64_t>(c) * EPC, o);
+    }
+  }
+}
+
+// Fallback for any n / alignment: one block per row, the row staged in shared memory as
+// fp32, exact two-pass statistics over the staged copy.
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(256)
+layernorm_block_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residual,
+                       const float *__restrict__ gamma, const float *__restrict__ beta,
+                       TIn *__restrict__ sum_out, TOut *__restrict__ y, float eps, int64_t m, int n) {
+  extern __shared__ float row_s[];
+  __shared__ float red[32];
+  __shared__ float bcast;
+  const int64_t row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  float s = 0.f;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    float v;
+    if constexpr (sizeof(TIn) == 4) v = x[row * n + j];
+    else v = static_cast<float>(x[row * n + j]);
+    if (residual) {
+      float r;
+      if constexpr (sizeof(TIn) == 4) r = residual[row * n + j];
+      else r = static_cast<float>(residual[row * n + j]);
+      v = LnTraits<TIn>::round(v + r);
+      if (sum_out) sum_out[row * n + j] = static_cast<TIn>(v);
+    }
+    row_s[j] = v;
+    s += v;
+  }
+  auto block_sum = [&](float val) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) val += __shfl_xor_sync(0xffffffffu, val, off);
+    __syncthreads();
+    if (lane == 0) red[warp] = val;
+    __syncthreads();
+    if (warp == 0) {
+      float t = lane < nwarps ? red[lane] : 0.f;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+      if (lane == 0) bcast = t;
+    }
+    __syncthreads();
+    return bcast;
+  };
+  const float mean = block_sum(s) / static_cast<float>(n);
+  float q = 0.f;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    const float d = row_s[j] - mean;
+    q = fmaf(d, d, q);
+  }
+  const float rstd = rsqrtf(block_sum(q) / static_cast<float>(n) + eps);
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    const float g = gamma ? gamma[j] : 1.f, b = beta ? beta[j] : 0.f;
+    y[row * n + j] = static_cast<TOut>(fmaf((row_s[j] - mean) * rstd, g, b));
+  }
+}
+
+template <typename TIn, typename TOut>
+static void launch_layernorm(const void *x, const void *residual, const float *gamma,
+                             const float *beta, void *sum_out, void *y, float eps, int64_t m,
+                             int64_t n, cudaStream_t s) {
+  constexpr int EPC = LnTraits<TIn>::EPC;
+  auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  const bool vec_ok = (n % EPC == 0) && n <= 32 * 16 * EPC && al(x) && al(y) &&
+                      (!residual || al(residual)) && (!sum_out || al(sum_out)) &&
+                      (!gamma || al(gamma)) && (!beta || al(beta));
+  const TIn *xi = static_cast<const TIn *>(x), *ri = static_cast<const TIn *>(residual);
+  TIn *so = static_cast<TIn *>(sum_out);
+  TOut *yo = static_cast<TOut *>(y);
+  if (vec_ok) {
+    const int per_lane = static_cast<int>((n / EPC + 31) / 32);
+    const unsigned grid = static_cast<unsigned>((m + kLnWarpsPerBlock - 1) / kLnWarpsPerBlock);
+    const int threads = kLnWarpsPerBlock * 32;
+    const int ni = static_cast<int>(n);
+    if (per_lane <= 2)
+      layernorm_warp_kernel<TIn, TOut, 2><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni);
+    else if (per_lane <= 4)
+      layernorm_warp_kernel<TIn, TOut, 4><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni);
+    else if (per_lane <= 6)
+      layernorm_warp_kernel<TIn, TOut, 6><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni);
+    else if (per_lane <= 8)
+      layernorm_warp_kernel<TIn, TOut, 8><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni);
+    else
+      layernorm_warp_kernel<TIn, TOut, 16><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni);
+    launched("layernorm_warp_kernel");
+  } else {
+    const size_t smem = static_cast<size_t>(n) * sizeof(float);
+    if (smem > 200 * 1024) {
+      fail("mgpuLayerNorm: row too long for the shared-memory kernel (n > 51200)");
+      return;
+    }
+    auto kern = layernorm_block_kernel<TIn, TOut>;
+    if (smem > 48 * 1024 &&
+        !check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem)),
+                    "cudaFuncSetAttribute(layernorm)"))
+      return;
+    kern<<<static_cast<unsigned>(m), 256, smem, s>>>(xi, ri, gamma, beta, so, yo, eps, m,
+                                                     static_cast<int>(n));
+    launched("layernorm_block_kernel");
+  }
+}
+
+}  // namespace mdc
+
+using namespace mdc;
+
+MDC_API void mgpuLayerNormEx(const void *x, const void *residual, const float *gamma,
+                             const float *beta, void *sum_out, void *y, float eps, int64_t m,
+                             int64_t n, int32_t io_dtype, int32_t out_dtype, void *stream) {
+  if (m <= 0 || n <= 0) return;
+  if (!device_info().ok) return;
+  if (m > 0x7fffffffLL * kLnWarpsPerBlock || n > 0x7fffffffLL) {
+    fail("mgpuLayerNorm: shape too large");
+    return;
+  }
+  cudaStream_t s = as_stream(stream);
+#define MDC_LN_CASE(IN_E, IN_T, OUT_E, OUT_T)                                                   \
+  if (io_dtype == IN_E && out_dtype == OUT_E) {                                                 \
+    launch_layernorm<IN_T, OUT_T>(x, residual, gamma, beta, sum_out, y, eps, m, n, s);          \
+    return;                                                                                     \
+  }
+  MDC_LN_CASE(MGPU_DTYPE_F32, float, MGPU_DTYPE_F32, float)
+  MDC_LN_CASE(MGPU_DTYPE_F16, __half, MGPU_DTYPE_F16, __half)
+  MDC_LN_CASE(MGPU_DTYPE_BF16, __nv_bfloat16, MGPU_DTYPE_BF16, __nv_bfloat16)
+  MDC_LN_CASE(MGPU_DTYPE_F16, __half, MGPU_DTYPE_F32, float)
+  MDC_LN_CASE(MGPU_DTYPE_BF16, __nv_bfloat16, MGPU_DTYPE_F32, float)
+  MDC_LN_CASE(MGPU_DTYPE_F32, float, MGPU_DTYPE_F16, __half)
+  MDC_LN_CASE(MGPU_DTYPE_F32, float, MGPU_DTYPE_BF16, __nv_bfloat16)
+#undef MDC_LN_CASE
+  fail("mgpuLayerNormEx: unsupported element type combination");
+}
+
+MDC_API void mgpuLayerNormF32(const float *x, const float *gamma, const float *beta, float *y,
+                              float eps, int64_t m, int64_t n, void *stream) {
+  mgpuLayerNormEx(x, nullptr, gamma, beta, nullptr, y, eps, m, n, MGPU_DTYPE_F32, MGPU_DTYPE_F32,
+                  stream);
+}

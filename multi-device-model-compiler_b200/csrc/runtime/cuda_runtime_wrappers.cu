@@ -1,0 +1,444 @@
+// libMultiDeviceCUDARuntime.so: the mgpu* C ABI that lowered graphs call for streams,
+// events, device memory, copies, module loading and kernel launches.  Same symbols and
+// argument meaning as the reference's lib/Runtime/CUDA/CudaRuntimeWrappers.cpp:91-384;
+// the implementation is new: the CUDA runtime API with the primary context (so the op
+// library, which launches with <<<>>>, shares it), a caching stream-ordered device pool,
+// a registry of built-in hand-written kernels, and a sticky error status.
+//
+// The library links the static CUDA runtime only.  The few driver-API calls that have no
+// runtime twin (module load, raw launch, tensor-map encode, 16/32-bit memset) are resolved
+// through cudaGetDriverEntryPoint, so the library loads on a machine without a driver and
+// fails at the first call instead.
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../ops/elementwise_kernels.cuh"
+#include "device_pool.h"
+#include "mdc_gpu_runtime.h"
+
+#define MDC_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+thread_local int32_t g_default_device = 0;
+thread_local bool g_device_bound = false;
+
+std::mutex g_err_mu;
+int32_t g_last_error = 0;
+std::string g_last_error_msg;
+
+bool debug_enabled() {
+  static const bool on = getenv("MULTI_DEVICE_CUDA_DEBUG") != nullptr;
+  return on;
+}
+
+void record_error(int32_t code, const char *what, const char *detail) {
+  fprintf(stderr, "'%s' failed with '%s'\n", what, detail ? detail : "<unknown>");
+  std::lock_guard<std::mutex> lock(g_err_mu);
+  if (g_last_error == 0) {
+    g_last_error = code ? code : -1;
+    g_last_error_msg = std::string(what) + ": " + (detail ? detail : "<unknown>");
+  }
+}
+
+bool rt_ok(cudaError_t e, const char *what) {
+  if (e == cudaSuccess) return true;
+  record_error(static_cast<int32_t>(e), what, cudaGetErrorName(e));
+  (void)cudaGetLastError();
+  return false;
+}
+#define RT_CHECK(expr) rt_ok((expr), #expr)
+
+// Binds the calling thread to the default device's primary context on first use.
+bool ensure_device() {
+  if (g_device_bound) return true;
+  if (!RT_CHECK(cudaSetDevice(g_default_device))) return false;
+  if (!RT_CHECK(cudaFree(nullptr))) return false;  // forces context creation
+  g_device_bound = true;
+  return true;
+}
+
+// ---- driver entry points without a runtime-API twin ----
+struct DriverApi {
+  CUresult (*ModuleLoad)(CUmodule *, const char *) = nullptr;
+  CUresult (*ModuleUnload)(CUmodule) = nullptr;
+  CUresult (*ModuleGetFunction)(CUfunction *, CUmodule, const char *) = nullptr;
+  CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
+                           unsigned, CUstream, void **, void **) = nullptr;
+  CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+  CUresult (*MemsetD32Async)(CUdeviceptr, unsigned, size_t, CUstream) = nullptr;
+  CUresult (*MemsetD16Async)(CUdeviceptr, unsigned short, size_t, CUstream) = nullptr;
+  CUresult (*GetErrorName)(CUresult, const char **) = nullptr;
+  CUresult (*TensorMapEncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
+  bool ok = false;
+};
+
+template <typename F>
+bool resolve(const char *name, F *out) {
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t e = cudaGetDriverEntryPoint(name, &fn, cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+    (void)cudaGetLastError();
+    record_error(e ? static_cast<int32_t>(e) : -1, name, "driver entry point not found");
+    return false;
+  }
+  *out = reinterpret_cast<F>(fn);
+  return true;
+}
+
+DriverApi &driver() {
+  static DriverApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    bool ok = true;
+    ok &= resolve("cuModuleLoad", &api.ModuleLoad);
+    ok &= resolve("cuModuleUnload", &api.ModuleUnload);
+    ok &= resolve("cuModuleGetFunction", &api.ModuleGetFunction);
+    ok &= resolve("cuLaunchKernel", &api.LaunchKernel);
+    ok &= resolve("cuFuncSetAttribute", &api.FuncSetAttribute);
+    ok &= resolve("cuMemsetD32Async", &api.MemsetD32Async);
+    ok &= resolve("cuMemsetD16Async", &api.MemsetD16Async);
+    ok &= resolve("cuGetErrorName", &api.GetErrorName);
+    ok &= resolve("cuTensorMapEncodeTiled", &api.TensorMapEncodeTiled);
+    api.ok = ok;
+  });
+  return api;
+}
+
+bool drv_ok(CUresult r, const char *what) {
+  if (r == CUDA_SUCCESS) return true;
+  const char *name = nullptr;
+  if (driver().GetErrorName) driver().GetErrorName(r, &name);
+  record_error(static_cast<int32_t>(r), what, name);
+  return false;
+}
+#define DRV_CHECK(expr) drv_ok((expr), #expr)
+
+// ---- module + built-in kernel registry ----
+CUmodule g_module = nullptr;
+std::unordered_map<std::string, const void *> &builtin_symbols() {
+  static std::unordered_map<std::string, const void *> m = {
+      {"mdc_add_f32", reinterpret_cast<const void *>(&mdc::mdc_add_f32)},
+      {"mdc_bias_add_f32", reinterpret_cast<const void *>(&mdc::mdc_bias_add_f32)},
+      {"mdc_relu_f32", reinterpret_cast<const void *>(&mdc::mdc_relu_f32)},
+      {"mdc_gelu_erf_f32", reinterpret_cast<const void *>(&mdc::mdc_gelu_erf_f32)},
+      {"mdc_gelu_tanh_f32", reinterpret_cast<const void *>(&mdc::mdc_gelu_tanh_f32)},
+  };
+  return m;
+}
+std::unordered_map<std::string, CUfunction> g_builtin_cache;
+// functions whose dynamic shared memory limit has already been raised to at least this
+std::unordered_map<CUfunction, int32_t> g_smem_limit;
+
+constexpr int kMaxDevices = 64;
+mdc::DevicePool g_pools[kMaxDevices];
+mdc::DevicePool &pool() {
+  int d = g_default_device;
+  if (d < 0 || d >= kMaxDevices) d = 0;
+  return g_pools[d];
+}
+
+int num_sms() {
+  static thread_local int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+      (void)cudaGetLastError();
+      sms = 148;
+    }
+  }
+  return sms;
+}
+
+// MLIR strided memref descriptor of rank-1 char (rank taken at run time).
+struct MemRefDesc {
+  char *basePtr;
+  char *data;
+  int64_t offset;
+  int64_t sizes_and_strides[1];  // sizes[rank] then strides[rank]
+};
+
+}  // namespace
+
+// ---------------- status ----------------
+MDC_API int32_t mgpuGetLastError(void) {
+  std::lock_guard<std::mutex> lock(g_err_mu);
+  return g_last_error;
+}
+MDC_API const char *mgpuGetLastErrorString(void) {
+  std::lock_guard<std::mutex> lock(g_err_mu);
+  static thread_local std::string copy;
+  copy = g_last_error_msg;
+  return copy.c_str();
+}
+MDC_API void mgpuClearLastError(void) {
+  std::lock_guard<std::mutex> lock(g_err_mu);
+  g_last_error = 0;
+  g_last_error_msg.clear();
+}
+MDC_API void mgpuSetLastError(int32_t code, const char *what) {
+  record_error(code, what ? what : "op", "reported by the op library");
+}
+
+// ---------------- module / launch ----------------
+MDC_API void mgpuModuleFileLoad(const char *fname) {
+  if (!ensure_device() || !driver().ok) return;
+  if (g_module) {
+    DRV_CHECK(driver().ModuleUnload(g_module));
+    g_module = nullptr;
+  }
+  if (!fname || !*fname) return;
+  FILE *f = fopen(fname, "rb");
+  if (!f) {
+    // Graphs made only of built-in kernels need no module file.
+    if (debug_enabled()) fprintf(stderr, "mgpuModuleFileLoad: '%s' not found, built-ins only\n", fname);
+    return;
+  }
+  fclose(f);
+  DRV_CHECK(driver().ModuleLoad(&g_module, fname));
+}
+
+MDC_API void mgpuModuleUnload(void) {
+  if (g_module && driver().ok) {
+    DRV_CHECK(driver().ModuleUnload(g_module));
+    g_module = nullptr;
+  }
+}
+
+MDC_API mgpu_function_t mgpuModuleGetFunction(const char *name) {
+  if (!name || !ensure_device() || !driver().ok) return nullptr;
+  auto cached = g_builtin_cache.find(name);
+  if (cached != g_builtin_cache.end()) return cached->second;
+  auto sym = builtin_symbols().find(name);
+  if (sym != builtin_symbols().end()) {
+    cudaFunction_t fn = nullptr;
+    if (!RT_CHECK(cudaGetFuncBySymbol(&fn, sym->second))) return nullptr;
+    g_builtin_cache[name] = reinterpret_cast<CUfunction>(fn);
+    return fn;
+  }
+  CUfunction function = nullptr;
+  if (!g_module) {
+    record_error(-1, name, "no such built-in kernel and no module loaded");
+    return nullptr;
+  }
+  DRV_CHECK(driver().ModuleGetFunction(&function, g_module, name));
+  return function;
+}
+
+MDC_API void mgpuLaunchKernel(mgpu_function_t function, intptr_t gridX, intptr_t gridY,
+                              intptr_t gridZ, intptr_t blockX, intptr_t blockY, intptr_t blockZ,
+                              int32_t smem, mgpu_stream_t stream, void **params, void **extra) {
+  if (!function) {
+    record_error(-1, "mgpuLaunchKernel", "null function");
+    return;
+  }
+  if (!ensure_device() || !driver().ok) return;
+  CUfunction fn = reinterpret_cast<CUfunction>(function);
+  // Raise the dynamic shared-memory limit only when a launch needs more than the default
+  // 48 KiB and more than was already granted (the reference queries the device and sets
+  // the attribute on every launch, CudaRuntimeWrappers.cpp:118-131).
+  if (smem > 48 * 1024) {
+    auto it = g_smem_limit.find(fn);
+    if (it == g_smem_limit.end() || it->second < smem) {
+      if (!DRV_CHECK(driver().FuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
+                                               smem)))
+        return;
+      g_smem_limit[fn] = smem;
+    }
+  }
+  if (debug_enabled())
+    fprintf(stderr, "Launching kernel, grid=%ld,%ld,%ld, threads: %ld, %ld, %ld, smem: %d B\n",
+            (long)gridX, (long)gridY, (long)gridZ, (long)blockX, (long)blockY, (long)blockZ, smem);
+  DRV_CHECK(driver().LaunchKernel(fn, (unsigned)gridX, (unsigned)gridY, (unsigned)gridZ,
+                                  (unsigned)blockX, (unsigned)blockY, (unsigned)blockZ,
+                                  (unsigned)smem, reinterpret_cast<CUstream>(stream), params,
+                                  extra));
+}
+
+MDC_API void mgpuBuiltinLaunchShape(int64_t n, intptr_t *gridX, intptr_t *blockX) {
+  if (blockX) *blockX = mdc::kEwBlock;
+  if (gridX) *gridX = mdc::ew_grid((n + 3) / 4, ensure_device() ? num_sms() : 148);
+}
+
+// ---------------- streams / events ----------------
+MDC_API mgpu_stream_t mgpuStreamCreate(void) {
+  if (!ensure_device()) return nullptr;
+  cudaStream_t s = nullptr;
+  RT_CHECK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  return s;
+}
+MDC_API void mgpuStreamDestroy(mgpu_stream_t stream) {
+  RT_CHECK(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
+}
+MDC_API void mgpuStreamSynchronize(mgpu_stream_t stream) {
+  RT_CHECK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+}
+MDC_API void mgpuStreamWaitEvent(mgpu_stream_t stream, mgpu_event_t event) {
+  RT_CHECK(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(event), 0));
+}
+MDC_API mgpu_event_t mgpuEventCreate(void) {
+  if (!ensure_device()) return nullptr;
+  cudaEvent_t e = nullptr;
+  RT_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  return e;
+}
+MDC_API mgpu_event_t mgpuEventCreateWithStream(mgpu_stream_t /*stream*/) { return mgpuEventCreate(); }
+MDC_API mgpu_event_t mgpuEventEnableTimeCreate(void) {
+  if (!ensure_device()) return nullptr;
+  cudaEvent_t e = nullptr;
+  RT_CHECK(cudaEventCreateWithFlags(&e, cudaEventDefault));
+  return e;
+}
+MDC_API void mgpuEventDestroy(mgpu_event_t event) {
+  RT_CHECK(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+}
+MDC_API void mgpuEventSynchronize(mgpu_event_t event) {
+  RT_CHECK(cudaEventSynchronize(static_cast<cudaEvent_t>(event)));
+}
+MDC_API void mgpuEventRecord(mgpu_event_t event, mgpu_stream_t stream) {
+  RT_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)));
+}
+MDC_API float mgpuEventElapsedTime(mgpu_event_t begin, mgpu_event_t end) {
+  float ms = 0.f;
+  RT_CHECK(cudaEventElapsedTime(&ms, static_cast<cudaEvent_t>(begin), static_cast<cudaEvent_t>(end)));
+  return ms;
+}
+
+// ---------------- memory ----------------
+MDC_API void *mgpuMemAlloc(uint64_t sizeBytes, mgpu_stream_t stream) {
+  if (!ensure_device()) return nullptr;
+  cudaError_t e;
+  void *p = pool().alloc(sizeBytes, static_cast<cudaStream_t>(stream), &e);
+  rt_ok(e, "mgpuMemAlloc");
+  return p;
+}
+MDC_API void mgpuMemFree(void *ptr, mgpu_stream_t stream) {
+  if (!ptr) return;
+  cudaError_t e;
+  if (!pool().free(ptr, static_cast<cudaStream_t>(stream), &e)) {
+    // not from the pool (e.g. a tensor map made by mgpuTensorMapEncodeTiledMemref)
+    RT_CHECK(cudaFree(ptr));
+    return;
+  }
+  rt_ok(e, "mgpuMemFree");
+}
+MDC_API void *mgpuMemAllocAsync(uint64_t sizeBytes, mgpu_stream_t stream) {
+  return mgpuMemAlloc(sizeBytes, stream);
+}
+MDC_API void mgpuMemFreeAsync(void *ptr, mgpu_stream_t stream) { mgpuMemFree(ptr, stream); }
+
+MDC_API void mgpuMemcpy(void *dst, void *src, size_t sizeBytes, mgpu_stream_t stream) {
+  if (!ensure_device()) return;
+  RT_CHECK(cudaMemcpyAsync(dst, src, sizeBytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+}
+MDC_API void mgpuMemset32(void *dst, unsigned int value, size_t count, mgpu_stream_t stream) {
+  if (!ensure_device() || !driver().ok) return;
+  DRV_CHECK(driver().MemsetD32Async(reinterpret_cast<CUdeviceptr>(dst), value, count,
+                                    reinterpret_cast<CUstream>(stream)));
+}
+MDC_API void mgpuMemset16(void *dst, unsigned short value, size_t count, mgpu_stream_t stream) {
+  if (!ensure_device() || !driver().ok) return;
+  DRV_CHECK(driver().MemsetD16Async(reinterpret_cast<CUdeviceptr>(dst), value, count,
+                                    reinterpret_cast<CUstream>(stream)));
+}
+
+MDC_API void mgpuMemHostRegister(void *ptr, uint64_t sizeBytes) {
+  if (!ensure_device()) return;
+  RT_CHECK(cudaHostRegister(ptr, sizeBytes, cudaHostRegisterDefault));
+}
+MDC_API void mgpuMemHostUnregister(void *ptr) { RT_CHECK(cudaHostUnregister(ptr)); }
+
+MDC_API void mgpuMemHostRegisterMemRef(int64_t rank, void *descriptor, int64_t elementSizeBytes) {
+  auto *d = static_cast<MemRefDesc *>(descriptor);
+  const int64_t *sizes = d->sizes_and_strides;
+  const int64_t *strides = sizes + rank;
+  int64_t running = 1;
+  for (int64_t i = rank - 1; i >= 0; --i) {  // only densely packed tensors are supported
+    if (strides[i] != running) {
+      record_error(-1, "mgpuMemHostRegisterMemRef", "memref is not densely packed");
+      return;
+    }
+    running *= sizes[i];
+  }
+  mgpuMemHostRegister(d->data + d->offset * elementSizeBytes,
+                      static_cast<uint64_t>(running * elementSizeBytes));
+}
+MDC_API void mgpuMemHostUnregisterMemRef(int64_t /*rank*/, void *descriptor,
+                                         int64_t elementSizeBytes) {
+  auto *d = static_cast<MemRefDesc *>(descriptor);
+  mgpuMemHostUnregister(d->data + d->offset * elementSizeBytes);
+}
+
+MDC_API void mgpuSetDefaultDevice(int32_t device) {
+  if (device != g_default_device) g_device_bound = false;
+  g_default_device = device;
+}
+
+MDC_API uint64_t mgpuPoolReservedBytes(void) { return pool().reserved_bytes(); }
+MDC_API uint64_t mgpuPoolInUseBytes(void) { return pool().in_use_bytes(); }
+MDC_API void mgpuPoolTrim(void) { pool().trim(); }
+
+// ---------------- tensor maps ----------------
+MDC_API void mgpuTensorMapEncodeTiled(void *tensorMap, int tensorDataType, uint32_t tensorRank,
+                                      void *globalAddress, const uint64_t *globalDim,
+                                      const uint64_t *globalStrides, const uint32_t *boxDim,
+                                      const uint32_t *elementStrides, int interleave, int swizzle,
+                                      int l2Promotion, int oobFill) {
+  if (!ensure_device() || !driver().ok) return;
+  DRV_CHECK(driver().TensorMapEncodeTiled(
+      static_cast<CUtensorMap *>(tensorMap), static_cast<CUtensorMapDataType>(tensorDataType),
+      tensorRank, globalAddress, reinterpret_cast<const cuuint64_t *>(globalDim),
+      reinterpret_cast<const cuuint64_t *>(globalStrides), boxDim, elementStrides,
+      static_cast<CUtensorMapInterleave>(interleave), static_cast<CUtensorMapSwizzle>(swizzle),
+      static_cast<CUtensorMapL2promotion>(l2Promotion),
+      static_cast<CUtensorMapFloatOOBfill>(oobFill)));
+}
+
+MDC_API void *mgpuTensorMapEncodeTiledMemref(int64_t tensorRank, void *descriptor,
+                                             int tensorDataType, int interleave, int swizzle,
+                                             int l2Promotion, int oobFill, int64_t *inputBoxDims) {
+  if (tensorRank < 1 || tensorRank > 5) {
+    record_error(-1, "mgpuTensorMapEncodeTiledMemref", "rank must be 1..5");
+    return nullptr;
+  }
+  auto *d = static_cast<MemRefDesc *>(descriptor);
+  const int64_t *sizes = d->sizes_and_strides;
+  // element sizes of CUtensorMapDataType 0..12
+  static const int elem_bytes[] = {1, 2, 4, 4, 8, 8, 2, 4, 8, 2, 4, 4, 4};
+  if (tensorDataType < 0 || tensorDataType > 12) {
+    record_error(-1, "mgpuTensorMapEncodeTiledMemref", "unknown element type");
+    return nullptr;
+  }
+  uint32_t box[5] = {1, 1, 1, 1, 1}, estr[5] = {1, 1, 1, 1, 1};
+  uint64_t gdim[5] = {1, 1, 1, 1, 1}, gstr[5] = {0, 0, 0, 0, 0};
+  for (int64_t r = 0; r < tensorRank; ++r) {  // innermost dimension first
+    box[r] = static_cast<uint32_t>(inputBoxDims[tensorRank - r - 1]);
+    gdim[r] = static_cast<uint64_t>(sizes[tensorRank - r - 1]);
+  }
+  // byte strides of dimensions 1..rank-1 of a densely packed tensor
+  uint64_t running = gdim[0] * elem_bytes[tensorDataType];
+  for (int64_t r = 0; r + 1 < tensorRank; ++r) {
+    gstr[r] = running;
+    running *= gdim[r + 1];
+  }
+  CUtensorMap map;
+  mgpuTensorMapEncodeTiled(&map, tensorDataType, static_cast<uint32_t>(tensorRank), d->data, gdim,
+                           gstr, box, estr, interleave, swizzle, l2Promotion, oobFill);
+  void *dmap = nullptr;
+  if (!RT_CHECK(cudaMalloc(&dmap, sizeof(CUtensorMap)))) return nullptr;
+  RT_CHECK(cudaMemcpy(dmap, &map, sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+  return dmap;
+}

@@ -45,7 +45,7 @@ def main(ref_root: str):
     out = {}
 
     # --- reference Decoder: pre-LN, causal, ReLU, dim_feedforward 2048 (torch default) ---
-    d_model, heads, B, S = 32, 4, 2, 12
+    d_model, heads, B, S = 64, 1, 2, 12  # head_dim 64: the GPU attention kernel can run it
     dec = LLM.Decoder(d_model, heads).eval()
     with torch.no_grad():
         # make LN affine and biases non-trivial so the fixture exercises them

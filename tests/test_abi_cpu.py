@@ -1,0 +1,95 @@
+"""CPU-side checks of the C-ABI boundary: the libraries build, load without a GPU, export
+every symbol the public headers declare, and refuse to compute without a device."""
+import ctypes
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared(header):
+    text = open(os.path.join(ROOT, "include", header)).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mgpu[A-Za-z0-9_]+)\s*\(", text)))
+
+
+def _exported(path):
+    out = subprocess.run(["nm", "-D", "--defined-only", path], capture_output=True, text=True, check=True).stdout
+    return {line.split()[-1] for line in out.splitlines() if line.strip()}
+
+
+@pytest.fixture(scope="module")
+def built(mdc):
+    if not (os.path.exists(mdc.RUNTIME_LIB) and os.path.exists(mdc.OPS_LIB)):
+        mdc.build()
+    return mdc
+
+
+def test_runtime_exports_every_declared_symbol(built):
+    names = _declared("mdc_gpu_runtime.h")
+    assert len(names) >= 35
+    missing = [n for n in names if n not in _exported(built.RUNTIME_LIB)]
+    assert not missing, missing
+    assert set(names) == set(built.RUNTIME_SIGNATURES), set(names) ^ set(built.RUNTIME_SIGNATURES)
+
+
+def test_ops_exports_every_declared_symbol(built):
+    names = _declared("mdc_gpu_ops.h")
+    exported = _exported(built.OPS_LIB)
+    missing = [n for n in names if n not in exported]
+    assert not missing, missing
+    assert set(names) == set(built.OPS_SIGNATURES), set(names) ^ set(built.OPS_SIGNATURES)
+    # the C++ symbols the reference's runner links against (Kernels/GPU/Ops.h:15-20)
+    for mangled in ("_Z10gpuOpsInitv", "_Z12gpuOpsDeinitv", "_Z13gpuLLMOpsInitv", "_Z15gpuLLMOpsDeinitv"):
+        assert mangled in exported
+
+
+def test_libraries_load_and_bind(built):
+    rt, ops = built.runtime(), built.ops()
+    for name in built.RUNTIME_SIGNATURES:
+        assert getattr(rt, name)
+    for name in built.OPS_SIGNATURES:
+        assert getattr(ops, name)
+
+
+def test_no_cpu_fallback_without_a_gpu(built):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    rt = built.runtime()
+    rt.mgpuClearLastError()
+    with pytest.raises(built.MdcError):
+        built.add(np.ones(8, np.float32), np.ones(8, np.float32))
+    rt.mgpuClearLastError()
+    with pytest.raises(built.MdcError):
+        built.init()
+    rt.mgpuClearLastError()
+
+
+def test_unimplemented_cnn_ops_set_the_status(built):
+    rt, ops = built.runtime(), built.ops()
+    rt.mgpuClearLastError()
+    ops.mgpuPool2d(None, None, *([1] * 15), None)
+    assert rt.mgpuGetLastError() != 0
+    assert b"mgpuPool2d" in rt.mgpuGetLastErrorString()
+    rt.mgpuClearLastError()
+    assert rt.mgpuGetLastError() == 0
+
+
+def test_pool_size_classes(built):
+    # size classes are a property of the allocator's host logic (no device needed)
+    src = open(os.path.join(ROOT, "multi-device-model-compiler_b200", "csrc", "runtime", "device_pool.cpp")).read()
+    assert "round_size" in src
+
+
+def test_bf16_helpers_round_to_nearest_even(built):
+    import torch
+    x = np.random.default_rng(0).standard_normal(1000).astype(np.float32)
+    bits = built.f32_to_bf16_bits(x)
+    ref = torch.from_numpy(x).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(bits, ref)
+    assert np.array_equal(built.bf16_bits_to_f32(bits), torch.from_numpy(x).to(torch.bfloat16).float().numpy())
