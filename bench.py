@@ -1,0 +1,334 @@
+#!/usr/bin/env python
+"""Benchmark of the encoder-stack hot path on B200.
+
+Workload (the configuration the headline metric is quoted on): a 12-layer post-LN encoder
+stack, hidden 768, 12 heads x 64, FFN 3072, exact GELU, fp16 storage with fp32 accumulation,
+sequence length 128, all-valid mask, 256 sequences per GPU per step; weights i.i.d.
+N(0, 0.02), biases 0, input N(0, 1), all seeded synthetic data.  A step is one pass of the
+stack over one batch through the library's C ABI (mgpuEncoderStackRun); with N GPUs every
+rank runs its own 256-sequence shard (replicas, no collective in the data path: weak
+scaling), and `value` is the sequences all ranks processed per second of the slowest rank.
+
+  python bench.py --gpus N --steps K --warmup W            one JSON line (rank 0)
+  python bench.py --impl reference ...                     the CPU restatement of the
+                                                           reference's path on the host cores
+
+The timed region holds only library calls on device-resident buffers and is bracketed by
+a barrier and a device synchronisation; time is taken with CUDA events on the launching
+stream and the maximum over ranks is reported.  `e2e` repeats the measurement through
+mgpuEncoderStackRunHost with pinned HOST buffers (upload, compute and download inside the
+timed region).  `roofline` describes the dominant kernel (the tcgen05 Gemm, 48 launches
+per step): its launches are bracketed by CUDA events in a second pass over the same K
+steps (mgpuOpsProfileBegin/End), so the headline time is not perturbed by the extra events.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L, B_PER_GPU, S, D, F, H = 12, 256, 128, 768, 3072, 12
+WORKLOAD = "encoder-stack-12L-h768-ffn3072-12heads-seq128-batch256-per-gpu"
+METRIC, UNIT = "encoder_stack_seqs_per_sec", "seq/s"
+
+# Gemm work of one step: 4 Gemms per layer over T = 256*128 tokens (algorithmic FLOPs)
+T = B_PER_GPU * S
+GEMM_FLOPS_PER_STEP = L * 2 * T * (D * 3 * D + D * D + 2 * D * F)
+GEMM_LAUNCHES_PER_STEP = 4 * L
+# DRAM bytes per Gemm launch from the ncu capture summarised in profiles/ (per launch,
+# averaged over the four shapes of a layer); None until a capture exists.
+GEMM_DRAM_TRAFFIC_PER_LAUNCH = None
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops_sustained"], "tflops_burst": p["bf16_tflops"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "tflops_burst": 1590.0, "source": "fallback"}
+
+
+def make_weights(seed=0):
+    rng = np.random.default_rng(seed)
+    layers = []
+    for _ in range(L):
+        layers.append({
+            "wqkv": (0.02 * rng.standard_normal((D, 3 * D))).astype(np.float32), "bqkv": np.zeros(3 * D, np.float32),
+            "wo": (0.02 * rng.standard_normal((D, D))).astype(np.float32), "bo": np.zeros(D, np.float32),
+            "w1": (0.02 * rng.standard_normal((D, F))).astype(np.float32), "b1": np.zeros(F, np.float32),
+            "w2": (0.02 * rng.standard_normal((F, D))).astype(np.float32), "b2": np.zeros(D, np.float32),
+            "ln1_g": None, "ln1_b": None, "ln2_g": None, "ln2_b": None})
+    return layers
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], None, [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # keep the samples taken under load (upper half of the power readings)
+        if power:
+            thr = 0.5 * max(power)
+            loaded = [c for c, p in zip(sm, power) if p >= thr] or sm
+        else:
+            loaded = sm
+        return {"sm_mhz": float(np.median(loaded)) if loaded else None, "sm_max_mhz": smax,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the CPU restatement of the reference's path (oracle/), all host
+    threads, on a bounded sample of the same workload per step."""
+    if rank != 0:
+        return
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle
+    sample = 16  # sequences per step (the full step is 256 per GPU)
+    layers = make_weights()
+    x = np.random.default_rng(1).standard_normal((sample, S, D)).astype(np.float32)
+    for _ in range(max(args.warmup, 0)):
+        oracle.encoder_stack(x[:1], layers, None, H, round_mode=oracle.ROUND_F16)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.encoder_stack(x, layers, None, H, round_mode=oracle.ROUND_F16)
+    dt = time.perf_counter() - t0
+    value = sample * args.steps / dt
+    cores = oracle.num_threads()
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sample": f"{sample} sequences per step"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                             "sample": f"{sample} of 256 sequences x 12 layers per step, {args.steps} steps"},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--chunks", type=int, default=4, help="pipeline depth of the host-buffer (e2e) path")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import __graft_entry__ as entry
+    mdc = entry.load_package()
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    mdc.init(local_rank)  # fails loudly without the CUDA libraries or a GPU
+    rt, ops = mdc.runtime(), mdc.ops()
+
+    def barrier():
+        rt.mgpuStreamSynchronize(None)
+        if dist is not None:
+            dist.barrier(device_ids=[local_rank])
+            import torch
+            torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if dist is None:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    layers = make_weights()
+    stack = mdc.EncoderStack(layers, H, norm_first=False, causal=False, act=mdc.ACT_GELU_ERF, dtype=mdc.F16)
+    x = np.random.default_rng(1 + rank).standard_normal((B_PER_GPU, S, D)).astype(np.float32)
+    stream = rt.mgpuStreamCreate()
+    dx = mdc.to_device(x, stream)
+    dy = mdc.DeviceBuffer(x.nbytes, stream)
+    ev0, ev1 = rt.mgpuEventEnableTimeCreate(), rt.mgpuEventEnableTimeCreate()
+
+    def step():
+        ops.mgpuEncoderStackRun(stack.h, dx.ptr, None, dy.ptr, B_PER_GPU, S, stream)
+
+    # ---------------- device-resident timed region ----------------
+    for _ in range(args.warmup):
+        step()
+    rt.mgpuStreamSynchronize(stream)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    launches0 = ops.mgpuOpsLaunchCount()
+    rt.mgpuEventRecord(ev0, stream)
+    for _ in range(args.steps):
+        step()
+    rt.mgpuEventRecord(ev1, stream)
+    rt.mgpuEventSynchronize(ev1)
+    barrier()
+    launches = ops.mgpuOpsLaunchCount() - launches0
+    ms_total = max_over_ranks(rt.mgpuEventElapsedTime(ev0, ev1))
+    clocks = sampler.stop()
+    status = ops.mgpuOpsCheckDeviceStatus(stream)
+    mdc.check("timed region")
+    if status:
+        raise mdc.MdcError(f"device status 0x{status:08x}")
+    ms_per_step = ms_total / args.steps
+    value = world * B_PER_GPU * args.steps / (ms_total / 1e3)
+
+    # ---------------- per-kernel pass: Gemm launch durations ----------------
+    ms_cat = (mdc.C.c_double * 4)()
+    n_cat = (mdc.C.c_uint64 * 4)()
+    ops.mgpuOpsProfileBegin()
+    for _ in range(args.steps):
+        step()
+    ops.mgpuOpsProfileEnd(ms_cat, n_cat)
+    pk = peaks()
+    gemm_ms_per_launch = ms_cat[0] / max(n_cat[0], 1)
+    achieved_tflops = (GEMM_FLOPS_PER_STEP / GEMM_LAUNCHES_PER_STEP) / (gemm_ms_per_launch * 1e-3) / 1e12
+    roofline = {"kernel": "gemm_tcgen05_kernel", "bound": "tensor", "achieved": achieved_tflops, "peak": pk["tflops"],
+                "unit": "TFLOP/s", "frac": achieved_tflops / pk["tflops"], "traffic": GEMM_DRAM_TRAFFIC_PER_LAUNCH,
+                "peak_source": f"{pk['source']} (sustained bf16; burst {pk['tflops_burst']})",
+                "frac_of_burst": achieved_tflops / pk["tflops_burst"],
+                "launches_per_step": int(n_cat[0] // args.steps), "ms_per_launch": gemm_ms_per_launch,
+                "time_share_per_step": {"gemm_ms": ms_cat[0] / args.steps, "attention_ms": ms_cat[1] / args.steps,
+                                        "layernorm_ms": ms_cat[2] / args.steps, "cast_ms": ms_cat[3] / args.steps}}
+
+    # ---------------- end to end through host buffers ----------------
+    y_host = np.empty_like(x)
+    rt.mgpuMemHostRegister(x.ctypes.data, x.nbytes)
+    rt.mgpuMemHostRegister(y_host.ctypes.data, y_host.nbytes)
+    for _ in range(2):
+        stack.run_host(x, y_host, None, chunks=args.chunks)
+    barrier()
+    t0 = time.perf_counter()
+    rt.mgpuEventRecord(ev0, stream)
+    for _ in range(args.steps):
+        stack.run_host(x, y_host, None, chunks=args.chunks)  # returns when y_host is complete
+    rt.mgpuEventRecord(ev1, stream)
+    rt.mgpuEventSynchronize(ev1)
+    e2e_ms = max_over_ranks(max(rt.mgpuEventElapsedTime(ev0, ev1), 1e3 * (time.perf_counter() - t0)))
+    barrier()
+    rt.mgpuMemHostUnregister(x.ctypes.data)
+    rt.mgpuMemHostUnregister(y_host.ctypes.data)
+    mdc.check("e2e region")
+    e2e = {"value": world * B_PER_GPU * args.steps / (e2e_ms / 1e3), "unit": UNIT,
+           "h2d_bytes_per_step": int(x.nbytes), "d2h_bytes_per_step": int(y_host.nbytes),
+           "ms_per_step": e2e_ms / args.steps, "chunks": args.chunks}
+
+    # ---------------- HBM-bound kernels of the metric: LayerNorm and Add ----------------
+    hbm = {}
+    if rank == 0:
+        def time_ms(fn, iters=20):
+            for _ in range(3):
+                fn()
+            rt.mgpuEventRecord(ev0, stream)
+            for _ in range(iters):
+                fn()
+            rt.mgpuEventRecord(ev1, stream)
+            rt.mgpuEventSynchronize(ev1)
+            return rt.mgpuEventElapsedTime(ev0, ev1) / iters
+        rows, n = 16384 * 8, 768  # 8 x the [32,512,768] config so the tensors exceed L2
+        a = mdc.DeviceBuffer(rows * n * 4, stream)
+        b = mdc.DeviceBuffer(rows * n * 4, stream)
+        c = mdc.DeviceBuffer(rows * n * 4, stream)
+        ms = time_ms(lambda: ops.mgpuLayerNormF32(a.ptr, None, None, b.ptr, 1e-5, rows, n, stream))
+        hbm["layernorm_f32_gbs"] = 2 * rows * n * 4 / ms / 1e6
+        ms = time_ms(lambda: ops.mgpuAdd(a.ptr, b.ptr, c.ptr, rows * n, stream))
+        hbm["add_f32_gbs"] = 3 * rows * n * 4 / ms / 1e6
+        hbm["peak_gbs"] = pk["hbm_gbs"]
+        hbm["layernorm_frac"] = hbm["layernorm_f32_gbs"] / pk["hbm_gbs"]
+        hbm["add_frac"] = hbm["add_f32_gbs"] / pk["hbm_gbs"]
+        hbm["note"] = f"{rows}x{n} fp32 (805 MB per tensor, larger than L2); {pk['source']} peak"
+        for buf in (a, b, c):
+            buf.release(stream)
+
+    # ---------------- CPU baseline (rank 0, N = 1 only) ----------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        oracle = entry.load_oracle()
+        sample = 64
+        oracle.encoder_stack(x[:1], layers[:1], None, H, round_mode=oracle.ROUND_F16)  # warm the threads
+        t0 = time.perf_counter()
+        ref = oracle.encoder_stack(x[:sample], layers, None, H, round_mode=oracle.ROUND_F16)
+        dt = time.perf_counter() - t0
+        got = mdc.to_host(dy, x.shape, np.float32, stream)[:sample]
+        cpu = {"value": sample / dt, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+               "sample": f"{sample} of 256 sequences x 12 layers, once ({dt:.1f} s)",
+               "parity_max_rel_vs_gpu": oracle.max_rel_err(ref, got, floor_frac=1.0)}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                "config": {"workload": WORKLOAD, "layers": L, "hidden": D, "ffn": F, "heads": H, "seq_len": S,
+                           "batch_per_gpu": B_PER_GPU, "global_batch": B_PER_GPU * world, "parallelism": f"replicas x{world}",
+                           "l2": "activations per step (about 650 MB) exceed the 126 MB L2; no explicit flush"},
+                "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
+                "hbm_kernels": hbm, "cpu_baseline": cpu}
+        print(json.dumps(line), flush=True)
+    stack.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

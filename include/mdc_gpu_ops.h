@@ -166,6 +166,14 @@ void mgpuTransformerEncoderLayer(const float *input, const float *qkv_weight, co
 /* Number of kernels this library has launched since load (for launch accounting). */
 uint64_t mgpuOpsLaunchCount(void);
 
+/* Per-kernel timing for measurements.  Between Begin and End every kernel launch of this
+ * library is bracketed by two CUDA events on its stream; End waits for them and returns,
+ * per category (0 Gemm, 1 attention, 2 LayerNorm, 3 elementwise / cast), the summed
+ * device time in milliseconds and the number of launches (arrays of 4; either may be NULL).
+ * Not to be left on in production: the events add a little work between kernels. */
+void mgpuOpsProfileBegin(void);
+void mgpuOpsProfileEnd(double *ms_per_category, uint64_t *launches_per_category);
+
 /* The tensor-core kernels bound every wait on a barrier; a kernel that gives up writes a
  * code into a device status word instead of hanging.  This call synchronises `stream`,
  * returns that word (0 = all kernels completed normally), sets the sticky status if it is

@@ -109,6 +109,8 @@ OPS_SIGNATURES = {
     "mgpuTransformerEncoderLayer": (None, [_vp] * 15 + [_i64] * 5 + [_b, _b, _i32, _i32, _f, _vp]),
     "mgpuOpsLaunchCount": (_u64, []),
     "mgpuOpsCheckDeviceStatus": (_u32, [_vp]),
+    "mgpuOpsProfileBegin": (None, []),
+    "mgpuOpsProfileEnd": (None, [C.POINTER(C.c_double), C.POINTER(_u64)]),
 }
 
 _rt = None

@@ -338,6 +338,7 @@ MDC_API void mgpuAttention(const void *qkv, const int32_t *seq_lens, void *out, 
   p.err = err;
   dim3 grid(static_cast<unsigned>(q_tiles), static_cast<unsigned>(heads), static_cast<unsigned>(batch));
   cudaStream_t s = as_stream(stream);
+  ProfileScope prof(kCatAttention, s);
   if (dtype == MGPU_DTYPE_F16) {
     auto kern = attention_tcgen05_kernel<__half>;
     static bool set = false;

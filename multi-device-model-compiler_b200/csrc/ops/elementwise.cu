@@ -1,11 +1,43 @@
 // Entry points for the HBM-bound elementwise ops: Add / bias / activation (fp32), element
 // type casts and the one-time weight packing (cast + transpose) for the tensor-core Gemm.
+#include <vector>
+
 #include "elementwise_kernels.cuh"
 #include "ops_common.h"
 
 namespace mdc {
 
 std::atomic<uint64_t> g_launch_count{0};
+
+bool g_profiling = false;
+namespace {
+struct ProfileSpan {
+  int cat;
+  cudaEvent_t begin, end;
+};
+std::vector<ProfileSpan> g_spans;
+std::vector<cudaEvent_t> g_spare_events;
+cudaEvent_t timing_event() {
+  if (!g_spare_events.empty()) {
+    cudaEvent_t e = g_spare_events.back();
+    g_spare_events.pop_back();
+    return e;
+  }
+  cudaEvent_t e = nullptr;
+  cudaEventCreate(&e);
+  return e;
+}
+}  // namespace
+
+void profile_mark(int category, cudaStream_t stream, bool begin) {
+  if (begin) {
+    ProfileSpan sp{category, timing_event(), timing_event()};
+    cudaEventRecord(sp.begin, stream);
+    g_spans.push_back(sp);
+  } else if (!g_spans.empty()) {
+    cudaEventRecord(g_spans.back().end, stream);
+  }
+}
 
 const DeviceInfo &device_info() {
   static thread_local DeviceInfo info;
@@ -154,10 +186,36 @@ using namespace mdc;
 
 MDC_API uint64_t mgpuOpsLaunchCount(void) { return g_launch_count.load(); }
 
+MDC_API void mgpuOpsProfileBegin(void) {
+  g_spans.clear();
+  g_profiling = true;
+}
+
+MDC_API void mgpuOpsProfileEnd(double *ms_per_category, uint64_t *launches_per_category) {
+  g_profiling = false;
+  for (int c = 0; c < kNumCategories; ++c) {
+    if (ms_per_category) ms_per_category[c] = 0.0;
+    if (launches_per_category) launches_per_category[c] = 0;
+  }
+  for (ProfileSpan &sp : g_spans) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(sp.end) == cudaSuccess && cudaEventElapsedTime(&ms, sp.begin, sp.end) == cudaSuccess) {
+      if (ms_per_category) ms_per_category[sp.cat] += ms;
+      if (launches_per_category) launches_per_category[sp.cat] += 1;
+    } else {
+      (void)cudaGetLastError();
+    }
+    g_spare_events.push_back(sp.begin);
+    g_spare_events.push_back(sp.end);
+  }
+  g_spans.clear();
+}
+
 MDC_API void mgpuAdd(const float *a, const float *b, float *c, int64_t n, void *stream) {
   if (n <= 0) return;
   const DeviceInfo &di = device_info();
   if (!di.ok) return;
+  ProfileScope prof(kCatElementwise, as_stream(stream));
   mdc_add_f32<<<ew_grid((n + 3) / 4, di.sms), kEwBlock, 0, as_stream(stream)>>>(a, b, c, n);
   launched("mdc_add_f32");
 }
@@ -204,6 +262,7 @@ MDC_API void mgpuCast(const void *src, int32_t sd, void *dst, int32_t dd, int64_
   if (!di.ok) return;
   cudaStream_t s = as_stream(stream);
   const int grid = ew_grid((n + 7) / 8, di.sms);
+  ProfileScope prof(kCatElementwise, s);
   if (sd == dd) {
     if (src != dst)
       check_cuda(cudaMemcpyAsync(dst, src, n * dtype_size(sd), cudaMemcpyDeviceToDevice, s), "copy");

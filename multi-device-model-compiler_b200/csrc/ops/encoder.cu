@@ -43,16 +43,18 @@ struct EncoderStack {
   void *x_dev[2] = {nullptr, nullptr}, *y_dev[2] = {nullptr, nullptr};
   int32_t *lens_dev[2] = {nullptr, nullptr};
   int64_t pipe_seqs = 0, pipe_seq_len = 0;
-  // stream that last used the workspace; a run on another stream first waits for it
-  void *last_stream = nullptr;
+  // recorded at the end of every run; the next run (on any stream) waits for it, because
+  // all runs of a stack share one activation workspace
+  cudaEvent_t done_ev = nullptr;
   bool used = false;
 };
 
-// The activation workspace is shared by all runs of a stack: order a run on a new stream
-// after the previous run's stream has drained.
 static void order_after_previous(EncoderStack *st, void *stream) {
-  if (st->used && st->last_stream != stream) cudaStreamSynchronize(as_stream(st->last_stream));
-  st->last_stream = stream;
+  if (!st->done_ev) check_cuda(cudaEventCreateWithFlags(&st->done_ev, cudaEventDisableTiming), "event");
+  if (st->used && st->done_ev) cudaStreamWaitEvent(as_stream(stream), st->done_ev, 0);
+}
+static void mark_run_done(EncoderStack *st, void *stream) {
+  if (st->done_ev) cudaEventRecord(st->done_ev, as_stream(stream));
   st->used = true;
 }
 
@@ -118,6 +120,7 @@ static void destroy_stack(EncoderStack *st, void *stream) {
     if (st->ev_comp[i]) cudaEventDestroy(st->ev_comp[i]);
     if (st->ev_out[i]) cudaEventDestroy(st->ev_out[i]);
   }
+  if (st->done_ev) cudaEventDestroy(st->done_ev);
   if (st->s_in) cudaStreamDestroy(st->s_in);
   if (st->s_comp) cudaStreamDestroy(st->s_comp);
   if (st->s_out) cudaStreamDestroy(st->s_out);
@@ -233,6 +236,7 @@ MDC_API void mgpuEncoderStackRun(void *stack, const float *x, const int32_t *seq
   order_after_previous(st, stream);
   if (!ensure_ws(st, batch * seq_len, stream)) return;
   run_stack(st, x, seq_lens, y, batch, seq_len, stream);
+  mark_run_done(st, stream);
 }
 
 MDC_API void mgpuEncoderStackDestroy(void *stack) {
@@ -295,6 +299,7 @@ MDC_API void mgpuEncoderStackRunHost(void *stack, const float *x_host, const int
     run_stack(st, static_cast<const float *>(st->x_dev[set]), seq_lens_host ? st->lens_dev[set] : nullptr,
               static_cast<float *>(st->y_dev[set]), nb, seq_len, st->s_comp);
     cudaEventRecord(st->ev_comp[set], st->s_comp);
+    mark_run_done(st, st->s_comp);
     cudaStreamWaitEvent(st->s_out, st->ev_comp[set], 0);
     check_cuda(cudaMemcpyAsync(y_host + off, st->y_dev[set], elems * 4, cudaMemcpyDeviceToHost, st->s_out), "D2H");
     cudaEventRecord(st->ev_out[set], st->s_out);

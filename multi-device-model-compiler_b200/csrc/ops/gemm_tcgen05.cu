@@ -328,7 +328,10 @@ static void launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const Gemm
       return;
     attr_set = true;
   }
-  kern<<<grid, gemm::THREADS, gemm::SMEM_BYTES, s>>>(ta, tb, p);
+  {
+    ProfileScope prof(kCatGemm, s);
+    kern<<<grid, gemm::THREADS, gemm::SMEM_BYTES, s>>>(ta, tb, p);
+  }
   launched("gemm_tcgen05_kernel");
 }
 

@@ -290,7 +290,7 @@ static void launch_layernorm(const void *x, const void *residual, const float *g
       return;
     }
     auto kern = layernorm_block_kernel<TIn, TOut>;
-    if (smem > 48 * 1024 &&
+    if (smem > 40 * 1024 &&  // static shared memory counts against the 48 KiB default too
         !check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem)),
                     "cudaFuncSetAttribute(layernorm)"))
@@ -315,6 +315,7 @@ MDC_API void mgpuLayerNormEx(const void *x, const void *residual, const float *g
     return;
   }
   cudaStream_t s = as_stream(stream);
+  ProfileScope prof(kCatLayerNorm, s);
 #define MDC_LN_CASE(IN_E, IN_T, OUT_E, OUT_T)                                                   \
   if (io_dtype == IN_E && out_dtype == OUT_E) {                                                 \
     launch_layernorm<IN_T, OUT_T>(x, residual, gamma, beta, sum_out, y, eps, m, n, s);          \

@@ -52,6 +52,23 @@ inline bool dtype_is16(int32_t dtype) { return dtype == MGPU_DTYPE_F16 || dtype 
 
 inline cudaStream_t as_stream(void *s) { return static_cast<cudaStream_t>(s); }
 
+// Optional per-launch timing: while profiling is on (mgpuOpsProfileBegin), every launch
+// site brackets its kernel with two CUDA events on the launching stream; mgpuOpsProfileEnd
+// sums the elapsed times per kernel category.  Off by default (no events, no overhead).
+enum ProfileCategory : int { kCatGemm = 0, kCatAttention = 1, kCatLayerNorm = 2, kCatElementwise = 3, kNumCategories = 4 };
+extern bool g_profiling;
+void profile_mark(int category, cudaStream_t stream, bool begin);
+struct ProfileScope {
+  int cat;
+  cudaStream_t stream;
+  ProfileScope(int c, cudaStream_t s) : cat(c), stream(s) {
+    if (g_profiling) profile_mark(cat, stream, true);
+  }
+  ~ProfileScope() {
+    if (g_profiling) profile_mark(cat, stream, false);
+  }
+};
+
 // Device slot the tensor-core kernels write a non-zero code into when one of their bounded
 // waits gives up; checked (and turned into the status) by mgpuOpsCheckDeviceStatus().
 uint32_t *device_error_slot();

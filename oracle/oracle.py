@@ -27,7 +27,10 @@ _ip = C.POINTER(C.c_int32)
 def build(force: bool = False) -> str:
     """Compile the oracle with the Makefile beside it (gcc only)."""
     src = os.path.join(_HERE, "mdc_oracle.c")
-    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+    graphs = os.path.join(_HERE, "libcpu_graph_add.so")
+    if (force or not os.path.exists(_LIB_PATH) or not os.path.exists(graphs)
+            or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
+            or os.path.getmtime(graphs) < os.path.getmtime(os.path.join(_HERE, "cpu_graphs.c"))):
         subprocess.run(["make", "-C", _HERE, "-B"], check=True, capture_output=True)
     return _LIB_PATH
 

@@ -1,4 +1,11 @@
-"""GPU parity: the tcgen05 fused attention kernel against the CPU oracle (max-rel <= 2e-2)."""
+"""GPU parity: the tcgen05 fused attention kernel against the CPU oracle.
+
+Tolerance: max-rel <= 2e-2 where an element's error is divided by max(|ref|, rms(ref)).
+The floor is the rms (not a small fraction of it as for the Gemm) because the softmax
+weights are stored in 16 bits before the second matrix product: every output carries an
+absolute error of about 2^-11 (fp16) or 2^-8 (bf16) of the typical output magnitude however
+small the output itself is; the oracle's own 16-bit path differs from its fp32 path by the
+same amount, which `_case` checks as well."""
 import numpy as np
 import pytest
 
@@ -21,11 +28,15 @@ def _case(m, B, S, H, lens, causal, dt, seed=0):
     qkv = oracle.round_array(rng.standard_normal((B * S, 3, H, D)).astype(np.float32), rm)
     got = m.attention(qkv, lens, B, S, H, D, causal=causal, dtype=dt).reshape(B, S, H * D)
     ref = oracle.attention(qkv, lens, B, S, H, D, causal=causal, round_mode=rm).reshape(B, S, H * D)
+    ref32 = oracle.attention(qkv, lens, B, S, H, D, causal=causal).reshape(B, S, H * D)
     assert np.all(np.isfinite(got))
     for b in range(B):  # padded query rows carry no meaning
         n = S if lens is None else int(lens[b])
         if n:
-            assert oracle.max_rel_err(ref[b, :n], got[b, :n]) <= TOL, (b, n)
+            assert oracle.max_rel_err(ref[b, :n], got[b, :n], floor_frac=1.0) <= TOL, (b, n)
+            # no noisier than the oracle's own 16-bit path is against exact arithmetic
+            noise = np.max(np.abs(ref[b, :n] - ref32[b, :n]))
+            assert np.max(np.abs(got[b, :n] - ref32[b, :n])) <= 2.0 * noise + 1e-6, (b, n)
     return got, ref
 
 
@@ -72,4 +83,4 @@ def test_large_scores_do_not_overflow(m):
     got = m.attention(qkv, None, B, S, H, D)
     ref = oracle.attention(qkv, None, B, S, H, D, round_mode=oracle.ROUND_F16)
     assert np.all(np.isfinite(got))
-    assert oracle.max_rel_err(ref, got) <= TOL
+    assert oracle.max_rel_err(ref, got, floor_frac=1.0) <= TOL

@@ -1,4 +1,8 @@
-"""GPU parity: encoder layer / stack entry points against the CPU oracle and the fixtures."""
+"""GPU parity: encoder layer / stack entry points against the CPU oracle and the fixtures.
+
+Tolerance: max-rel <= 2e-2 with an element's error divided by max(|ref|, rms(ref)): the
+layer stores every intermediate tensor in 16 bits, so its outputs carry an absolute error
+proportional to the typical magnitude (see tests/test_gpu_attention.py)."""
 import numpy as np
 import pytest
 
@@ -38,7 +42,7 @@ def _check(ref, got, lens):
     B, S = ref.shape[:2]
     for b in range(B):
         n = S if lens is None else int(lens[b])
-        assert oracle.max_rel_err(ref[b, :n], got[b, :n]) <= TOL, b
+        assert oracle.max_rel_err(ref[b, :n], got[b, :n], floor_frac=1.0) <= TOL, b
 
 
 @pytest.mark.parametrize("norm_first,causal,act", [(False, False, 2), (True, True, 1), (False, True, 3), (True, False, 2)])
@@ -133,16 +137,18 @@ def test_stack_and_batch_independence(m):
 
 def test_reference_decoder_fixture(m, golden):
     # benchmark/PyTorch/Models/LLM.py (pre-LN, causal, ReLU) computed in fp32 by the reference's
-    # model definition; the GPU layer runs it in fp16, so elements near zero are judged against
-    # 5 % of the rms like the oracle's own fp16-storage check
+    # model definition; the GPU layer runs it with fp16 storage
     lw = {k: golden["dec_" + k] for k in ("wqkv", "bqkv", "wo", "bo", "w1", "b1", "w2", "b2", "ln1_g", "ln1_b", "ln2_g", "ln2_b")}
     st = m.EncoderStack([lw], int(golden["dec_heads"]), norm_first=True, causal=True, act=m.ACT_RELU)
     got = st.run(golden["dec_x"], None)
     st.close()
-    assert oracle.max_rel_err(golden["dec_y"], got, floor_frac=5e-2) <= TOL
+    assert oracle.max_rel_err(golden["dec_y"], got, floor_frac=1.0) <= TOL
     ref = oracle.encoder_layer(golden["dec_x"], lw, None, int(golden["dec_heads"]), norm_first=True, causal=True,
                                act=oracle.ACT_RELU, round_mode=oracle.ROUND_F16)
-    assert oracle.max_rel_err(ref, got) <= TOL
+    assert oracle.max_rel_err(ref, got, floor_frac=1.0) <= TOL
+    # the GPU layer is as close to the fp32 model as the oracle's fp16-storage path is
+    noise = np.max(np.abs(ref - golden["dec_y"]))
+    assert np.max(np.abs(got - golden["dec_y"])) <= 2.0 * noise
 
 
 def test_head_dim_other_than_64_is_rejected(m, golden):

@@ -87,7 +87,12 @@ def test_mgpu_matmul_reference_fixtures(m, golden):
     # benchmark/PyTorch/Models/Linear.py in the shape of test/End2End/GPU/linear.mlir
     y = m.activation(m.matmul(golden["lin_x"], golden["lin_w"], golden["lin_b"]), m.ACT_RELU)
     assert y.shape == golden["lin_y"].shape
-    assert oracle.max_rel_err(golden["lin_y"], y) <= TOL
+    ref16 = oracle.matmul(golden["lin_x"], golden["lin_w"], golden["lin_b"], round_mode=oracle.ROUND_F16,
+                          act=oracle.ACT_RELU)
+    assert oracle.max_rel_err(ref16, y) <= TOL
+    # against the fp32 model output the fp16 operand rounding shows: elements near zero are
+    # judged against 5 % of the rms (as in tests/test_oracle_golden.py)
+    assert oracle.max_rel_err(golden["lin_y"], y, floor_frac=5e-2) <= TOL
     # examples/genonnx.py:52-64: Gemm 20x10 . 10x20 (K not a multiple of 8)
     rng = np.random.default_rng(5)
     a, w = rng.standard_normal((20, 10)).astype(np.float32), rng.standard_normal((10, 20)).astype(np.float32)
@@ -107,4 +112,6 @@ def test_linearity_at_full_size(m):
     a2[:, :K // 2] = 0
     y = m.matmul16(a, w, out_dtype=m.F32)
     y12 = m.matmul16(a1, w, out_dtype=m.F32) + m.matmul16(a2, w, out_dtype=m.F32)
-    assert oracle.max_rel_err(y12, y) <= 1e-4
+    # equal up to the order of the fp32 accumulation
+    assert oracle.max_rel_err(y12, y) <= 5e-3
+    assert np.max(np.abs(y12 - y)) <= 1e-4
