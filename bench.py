@@ -154,8 +154,76 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+MICRO = {
+    # name: (kind, M-per-token-or-rows, N, K)   Gemm shapes of one layer + the standalone configs
+    "gemm_qkv": ("gemm", None, 3 * D, D), "gemm_proj": ("gemm", None, D, D),
+    "gemm_ffn1": ("gemm_gelu", None, F, D), "gemm_ffn2": ("gemm", None, D, F),
+    "gemm_c1": ("gemm", 2048, 4096, 4096),
+}
+
+
+def run_micro(args):
+    """One kernel, a few launches, on random data: the small case the ncu captures in
+    profiles/ are taken on.  Prints one JSON line with the CUDA-event time per launch."""
+    import __graft_entry__ as entry
+    mdc = entry.load_package()
+    mdc.init(0)
+    rt, ops = mdc.runtime(), mdc.ops()
+    rng = np.random.default_rng(0)
+    tokens = args.tokens
+    stream = rt.mgpuStreamCreate()
+    ev0, ev1 = rt.mgpuEventEnableTimeCreate(), rt.mgpuEventEnableTimeCreate()
+    name = args.micro
+    if name in MICRO:
+        kind, M, N, K = MICRO[name]
+        M = M or tokens
+        a = mdc.to_device(rng.standard_normal((M, K)).astype(np.float16), stream)
+        w = mdc.to_device((0.02 * rng.standard_normal((N, K))).astype(np.float16), stream)
+        bias = mdc.to_device(np.zeros(N, np.float32), stream)
+        out = mdc.DeviceBuffer(M * N * 2, stream)
+        act = mdc.ACT_GELU_ERF if kind == "gemm_gelu" else mdc.ACT_NONE
+        fn = lambda: ops.mgpuMatmulEx16(a.ptr, w.ptr, bias.ptr, None, out.ptr, M, N, K, mdc.F16, mdc.F16, act, stream)
+        work, unit = 2.0 * M * N * K, "TFLOP/s"
+    elif name == "attention":
+        Bq = max(tokens // S, 1)
+        q = mdc.to_device(rng.standard_normal((Bq * S, 3 * H * 64)).astype(np.float16), stream)
+        out = mdc.DeviceBuffer(Bq * S * H * 64 * 2, stream)
+        fn = lambda: ops.mgpuAttention(q.ptr, None, out.ptr, Bq, S, H, 64, False, mdc.F16, stream)
+        work, unit = 4.0 * Bq * H * S * S * 64, "TFLOP/s"
+    elif name in ("layernorm_f32", "add_f32"):
+        rows, n = tokens, args.hidden
+        a = mdc.to_device(rng.standard_normal((rows, n)).astype(np.float32), stream)
+        b = mdc.to_device(rng.standard_normal((rows, n)).astype(np.float32), stream)
+        c = mdc.DeviceBuffer(rows * n * 4, stream)
+        if name == "layernorm_f32":
+            fn = lambda: ops.mgpuLayerNormF32(a.ptr, None, None, c.ptr, 1e-5, rows, n, stream)
+            work, unit = 2.0 * rows * n * 4, "GB/s"
+        else:
+            fn = lambda: ops.mgpuAdd(a.ptr, b.ptr, c.ptr, rows * n, stream)
+            work, unit = 3.0 * rows * n * 4, "GB/s"
+    else:
+        raise SystemExit(f"unknown --micro {name}")
+    for _ in range(args.warmup):
+        fn()
+    rt.mgpuEventRecord(ev0, stream)
+    for _ in range(args.steps):
+        fn()
+    rt.mgpuEventRecord(ev1, stream)
+    rt.mgpuEventSynchronize(ev1)
+    ms = rt.mgpuEventElapsedTime(ev0, ev1) / args.steps
+    status = ops.mgpuOpsCheckDeviceStatus(stream)
+    mdc.check("micro")
+    rate = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    print(json.dumps({"micro": name, "tokens": tokens, "ms_per_launch": ms, "rate": rate, "unit": unit,
+                      "device_status": status}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--micro", default=None, help="run one kernel only (for profiling): " + ", ".join(
+        list(MICRO) + ["attention", "layernorm_f32", "add_f32"]))
+    ap.add_argument("--tokens", type=int, default=8192, help="--micro: rows / tokens of the small case")
+    ap.add_argument("--hidden", type=int, default=768, help="--micro layernorm_f32 / add_f32: row length")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -171,6 +239,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.micro:
+        run_micro(args)
         return
 
     import __graft_entry__ as entry

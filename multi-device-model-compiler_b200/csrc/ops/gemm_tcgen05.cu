@@ -11,7 +11,11 @@
 //            stage to the producer and, after the last k-block, hands the accumulator over.
 //   warps 2-9 epilogue: tcgen05.ld the 128 x 256 fp32 accumulator out of TMEM (each warp
 //            its 32-lane quarter, two warps per quarter splitting the columns), add bias,
-//            apply the activation, add the residual, convert and store.
+//            apply the activation, add the residual, convert.  Each warp stages 32 rows x
+//            128 bytes of output in swizzled shared memory and writes it with one TMA
+//            store, so global writes are full lines; the residual tile arrives the same
+//            way through a TMA load.  (Shapes whose rows are not 16-byte multiples fall
+//            back to direct stores.)
 // TMEM holds two accumulators (2 x 256 columns) so the epilogue of tile i overlaps the
 // mainloop of tile i+1.  No cluster launch and no multicast: every CTA fetches its own tiles
 // and relies on L2 for reuse.  All waits are bounded (see ptx_sm100.cuh).
@@ -25,14 +29,16 @@ namespace mdc {
 
 namespace gemm {
 constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;
 constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 64 + EPI_WARPS * 32;
 constexpr int TMEM_COLS = 512;
-constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024;  // + alignment slack
+constexpr int EPI_BUF_BYTES = 4096;  // 32 rows x 128 bytes, per warp, one for output and one for residual
+constexpr size_t SMEM_BYTES =
+    static_cast<size_t>(STAGES) * STAGE_BYTES + EPI_WARPS * 2 * EPI_BUF_BYTES + 1024;  // + alignment slack
 }  // namespace gemm
 
 struct GemmParams {
@@ -40,11 +46,25 @@ struct GemmParams {
   const float *bias;
   const void *residual;
   void *out;
+  int tma_epi;      // output (and residual) rows are 16-byte multiples: TMA-staged epilogue
   int out_vec_ok;   // rows of out / residual can be accessed with 16-byte vectors
   int bias_vec_ok;  // bias is 16-byte aligned
   int num_m_blocks, num_n_blocks;
   uint32_t *err;
+#ifdef MDC_GEMM_TRACE
+  unsigned long long *trace;  // [grid][8] cycle counters (debug builds only)
+  int dbg_mode;               // 1: loads only (no MMA issued); 2: MMA only (no loads issued)
+#endif
 };
+
+#ifdef MDC_GEMM_TRACE
+#define TRACE_T0() const long long _t0 = clock64()
+#define TRACE_ADD(slot) \
+  if (p.trace) atomicAdd(p.trace + blockIdx.x * 8 + (slot), (unsigned long long)(clock64() - _t0))
+#else
+#define TRACE_T0()
+#define TRACE_ADD(slot)
+#endif
 
 template <typename TOut>
 __device__ __forceinline__ void store_out8(TOut *dst, const float *v);
@@ -90,14 +110,38 @@ __device__ __forceinline__ void load_res8(const __nv_bfloat16 *src, float *v) {
   }
 }
 
+// Activation for the Gemm epilogue.  The exact-erf GELU uses the rational approximation
+// erf(x) = 1 - (a1 t + ... + a5 t^5) exp(-x^2), t = 1/(1 + p x) (Abramowitz & Stegun 7.1.26,
+// |error| <= 1.5e-7), a third of the instructions of erff(): the epilogue runs beside the
+// tensor pipe and must keep up with it, and the result is rounded to 16 bits anyway.
+template <int ACT>
+__device__ __forceinline__ float act_fast(float v) {
+  if constexpr (ACT == kActGeluErf) {
+    const float x = fabsf(v) * 0.70710678118654752440f;
+    const float t = __fdividef(1.0f, fmaf(0.3275911f, x, 1.0f));
+    float poly = fmaf(1.061405429f, t, -1.453152027f);
+    poly = fmaf(poly, t, 1.421413741f);
+    poly = fmaf(poly, t, -0.284496736f);
+    poly = fmaf(poly, t, 0.254829592f);
+    const float erf_abs = fmaf(-poly * t, __expf(-x * x), 1.0f);
+    const float h = 0.5f * v;
+    return fmaf(fabsf(h), erf_abs, h);  // 0.5 v (1 + sign(v) erf|x|)
+  } else {
+    return act_apply_t<ACT>(v);
+  }
+}
+
 template <typename T16, typename TOut, int ACT>
 __global__ void __launch_bounds__(gemm::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_out,
+                    const __grid_constant__ CUtensorMap tmap_res, const GemmParams p) {
   using namespace gemm;
   using namespace ptx;
   extern __shared__ uint8_t smem_dyn[];
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
+  __shared__ uint64_t res_bar[EPI_WARPS];
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t abort_flag_s;
   volatile uint32_t *abort_flag = &abort_flag_s;
@@ -121,6 +165,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       mbar_init(&acc_full_bar[a], 1);
       mbar_init(&acc_empty_bar[a], EPI_WARPS * 32);
     }
+    for (int w = 0; w < EPI_WARPS; ++w) mbar_init(&res_bar[w], 1);
     mbar_init_fence();
   }
   if (warp == 1) {
@@ -141,16 +186,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         const int m_blk = tile % p.num_m_blocks, n_blk = tile / p.num_m_blocks;
         for (int kb = 0; kb < num_kb; ++kb) {
+          { TRACE_T0();
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
             atomicCAS(p.err, 0u, 0x10000000u | static_cast<uint32_t>(stage));
             ok = false;
             break;
           }
+          TRACE_ADD(0); }
           uint8_t *sa = tiles + stage * STAGE_BYTES;
           uint8_t *sb = sa + A_BYTES;
+#ifdef MDC_GEMM_TRACE
+          if (p.dbg_mode == 2) { mbar_arrive(&full_bar[stage]); } else
+#endif
+          {
           mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
           tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m_blk * BM);
           tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n_blk * BN);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -166,22 +218,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        { TRACE_T0();
         if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
           atomicCAS(p.err, 0u, 0x30000000u | static_cast<uint32_t>(acc));
           break;
         }
+        TRACE_ADD(1); }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
+          { TRACE_T0();
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
             atomicCAS(p.err, 0u, 0x20000000u | static_cast<uint32_t>(stage));
             ok = false;
             break;
           }
+          TRACE_ADD(2); }
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
           const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
           const uint64_t b_desc = make_smem_desc_sw128(sa + A_BYTES, 16, 1024);
+#ifdef MDC_GEMM_TRACE
+          if (p.dbg_mode != 1)
+#endif
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // 16 k-elements = 32 bytes further along the 128-byte swizzled row
@@ -203,15 +262,104 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int half_sel = ew >> 2;   // which 128 accumulator columns this warp handles
     TOut *out = static_cast<TOut *>(p.out);
     const T16 *res = static_cast<const T16 *>(p.residual);
+    uint8_t *my_out = tiles + STAGES * STAGE_BYTES + ew * 2 * EPI_BUF_BYTES;
+    uint8_t *my_res = my_out + EPI_BUF_BYTES;
+    uint32_t res_phase = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       const int m_blk = tile % p.num_m_blocks, n_blk = tile / p.num_m_blocks;
+      { TRACE_T0();
       if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag)) {
         atomicCAS(p.err, 0u, 0x40000000u | static_cast<uint32_t>(acc));
         break;
       }
+      if (threadIdx.x == 64) { TRACE_ADD(3); } }
       tc_fence_after();
+      TRACE_T0();
+      if (p.tma_epi) {
+        // ---- staged path: 32 rows x CW columns (128 bytes of output per row) at a time ----
+        constexpr int CW = sizeof(TOut) == 2 ? 64 : 32;
+        constexpr int RES_ROW_BYTES = CW * 2;  // residual is 16-bit
+        const int row0 = m_blk * BM + quarter * 32;
+        const uint32_t lane_base = tmem_base + static_cast<uint32_t>(acc * BN) +
+                                   (static_cast<uint32_t>(quarter * 32) << 16);
+        bool chunk_ok = true;
+#pragma unroll 1
+        for (int chunk = 0; chunk < BN / 2 / CW && chunk_ok; ++chunk) {
+          const int col0 = half_sel * (BN / 2) + chunk * CW;
+          const int gcol0 = n_blk * BN + col0;
+          if (gcol0 >= p.N) break;  // uniform across the warp
+          if (res && lane == 0) {
+            mbar_arrive_expect_tx(&res_bar[ew], 32 * RES_ROW_BYTES);
+            tma_load_2d(my_res, &tmap_res, &res_bar[ew], gcol0, row0);
+          }
+          float v[CW];
+          {
+            uint32_t r[32];
+            tmem_ld_32x32(lane_base + col0, r);
+            if constexpr (CW == 64) {
+              uint32_t r2[32];
+              tmem_ld_32x32(lane_base + col0 + 32, r2);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[32 + j] = __uint_as_float(r2[j]);
+            } else {
+              tmem_ld_wait();
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          }
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < CW; j += 4) {
+              if (gcol0 + j < p.N) {  // N is a multiple of 4 on this path
+                const float4 b = __ldg(reinterpret_cast<const float4 *>(p.bias + gcol0 + j));
+                v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < CW; ++j) v[j] = act_fast<ACT>(v[j]);
+          if (res) {
+            if (!mbar_wait(&res_bar[ew], res_phase, abort_flag)) {
+              atomicCAS(p.err, 0u, 0x50000000u | static_cast<uint32_t>(ew));
+              chunk_ok = false;
+              break;
+            }
+            res_phase ^= 1;
+            // residual rows are RES_ROW_BYTES long; 16-byte pieces are XOR-swizzled like TMA wrote them
+#pragma unroll
+            for (int j = 0; j < RES_ROW_BYTES / 16; ++j) {
+              const int phys = RES_ROW_BYTES == 128 ? (j ^ (lane & 7)) : (j ^ ((lane >> 1) & 3));
+              float rv[8];
+              load_res8(reinterpret_cast<const T16 *>(my_res + lane * RES_ROW_BYTES + (phys << 4)), rv);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[8 * j + e] += rv[e];
+            }
+          }
+          // the previous TMA store must have finished reading the staging buffer
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+          constexpr int EPC = 16 / sizeof(TOut);  // elements per 16-byte piece
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint8_t *dst = my_out + lane * 128 + ((j ^ (lane & 7)) << 4);
+            if constexpr (sizeof(TOut) == 2) {
+              store_out8<TOut>(reinterpret_cast<TOut *>(dst), v + EPC * j);
+            } else {
+              *reinterpret_cast<float4 *>(dst) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_out, my_out, gcol0, row0);  // rows / columns past M / N are clipped
+            tma_store_commit();
+          }
+        }
+        if (!chunk_ok) break;
+      } else {
       const int row = m_blk * BM + quarter * 32 + lane;
       const bool row_ok = row < p.M;
 #pragma unroll 1
@@ -270,11 +418,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
+      }
       tc_fence_before();
       mbar_arrive(&acc_empty_bar[acc]);
+      if (threadIdx.x == 64) { TRACE_ADD(4); }
       if ((acc ^= 1) == 0) acc_phase ^= 1;
     }
+    if (lane == 0) tma_store_wait<0>();  // all staged output has left shared memory
   }
+#ifdef MDC_GEMM_TRACE
+  if (threadIdx.x == 0 && p.trace) p.trace[blockIdx.x * 8 + 7] = (unsigned long long)clock64();
+#endif
 
   // ------------------------------ teardown ------------------------------
   if (*abort_flag) {
@@ -290,6 +444,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 // ---------------------------------------------------------------------------------------
+#ifdef MDC_GEMM_TRACE
+static unsigned long long *g_gemm_trace = nullptr;
+static int g_gemm_dbg_mode = 0;
+#endif
 static uint32_t *g_err_slot = nullptr;
 
 uint32_t *device_error_slot() {
@@ -300,25 +458,32 @@ uint32_t *device_error_slot() {
   return g_err_slot;
 }
 
-bool encode_tmap_2d(CUtensorMap *map, const void *base, int32_t dtype, uint64_t inner, uint64_t outer,
-                    uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+// elem: MGPU_DTYPE_*; swizzle_bytes: 128 or 64 (must equal box_inner * element size)
+bool encode_tmap_2d_ex(CUtensorMap *map, const void *base, int32_t elem, uint64_t inner, uint64_t outer,
+                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, int swizzle_bytes) {
   const uint64_t gdim[2] = {inner, outer};
   const uint64_t gstr[1] = {row_stride_bytes};
   const uint32_t box[2] = {box_inner, box_outer};
   const uint32_t estr[2] = {1, 1};
   const int before = mgpuGetLastError();
-  mgpuTensorMapEncodeTiled(map,
-                           dtype == MGPU_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                    : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                           2, const_cast<void *>(base), gdim, gstr, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  const int dt = elem == MGPU_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                 : elem == MGPU_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  mgpuTensorMapEncodeTiled(map, dt, 2, const_cast<void *>(base), gdim, gstr, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return before != 0 || mgpuGetLastError() == 0;
 }
 
+bool encode_tmap_2d(CUtensorMap *map, const void *base, int32_t dtype, uint64_t inner, uint64_t outer,
+                    uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  return encode_tmap_2d_ex(map, base, dtype, inner, outer, row_stride_bytes, box_inner, box_outer, 128);
+}
+
 template <typename T16, typename TOut, int ACT>
-static void launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int grid,
-                        cudaStream_t s) {
+static void launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to,
+                        const CUtensorMap &tr, const GemmParams &p, int grid, cudaStream_t s) {
   auto kern = gemm_tcgen05_kernel<T16, TOut, ACT>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -330,19 +495,19 @@ static void launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const Gemm
   }
   {
     ProfileScope prof(kCatGemm, s);
-    kern<<<grid, gemm::THREADS, gemm::SMEM_BYTES, s>>>(ta, tb, p);
+    kern<<<grid, gemm::THREADS, gemm::SMEM_BYTES, s>>>(ta, tb, to, tr, p);
   }
   launched("gemm_tcgen05_kernel");
 }
 
 template <typename T16, typename TOut>
-static void launch_gemm_act(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p,
-                            int grid, int act, cudaStream_t s) {
+static void launch_gemm_act(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to,
+                            const CUtensorMap &tr, const GemmParams &p, int grid, int act, cudaStream_t s) {
   switch (act) {
-  case MGPU_ACT_NONE: launch_gemm<T16, TOut, kActNone>(ta, tb, p, grid, s); break;
-  case MGPU_ACT_RELU: launch_gemm<T16, TOut, kActRelu>(ta, tb, p, grid, s); break;
-  case MGPU_ACT_GELU_ERF: launch_gemm<T16, TOut, kActGeluErf>(ta, tb, p, grid, s); break;
-  case MGPU_ACT_GELU_TANH: launch_gemm<T16, TOut, kActGeluTanh>(ta, tb, p, grid, s); break;
+  case MGPU_ACT_NONE: launch_gemm<T16, TOut, kActNone>(ta, tb, to, tr, p, grid, s); break;
+  case MGPU_ACT_RELU: launch_gemm<T16, TOut, kActRelu>(ta, tb, to, tr, p, grid, s); break;
+  case MGPU_ACT_GELU_ERF: launch_gemm<T16, TOut, kActGeluErf>(ta, tb, to, tr, p, grid, s); break;
+  case MGPU_ACT_GELU_TANH: launch_gemm<T16, TOut, kActGeluTanh>(ta, tb, to, tr, p, grid, s); break;
   default: fail("mgpuMatmulEx16: unknown activation");
   }
 }
@@ -386,24 +551,46 @@ MDC_API void mgpuMatmulEx16(const void *a, const void *w_nk, const float *bias, 
   p.out_vec_ok = (N % out_vec == 0) && (N % 8 == 0) && !(reinterpret_cast<uintptr_t>(out) & 15u) &&
                  (!residual || !(reinterpret_cast<uintptr_t>(residual) & 15u));
   p.bias_vec_ok = bias && !(reinterpret_cast<uintptr_t>(bias) & 15u);
+  // staged (TMA) epilogue: rows of out / residual must be multiples of 16 bytes and the
+  // bias readable as float4
+  p.tma_epi = p.out_vec_ok && (!bias || p.bias_vec_ok);
+  CUtensorMap to = ta, tr = ta;  // placeholders when the direct-store epilogue is used
+  if (p.tma_epi) {
+    const uint32_t cw = out_elem == 2 ? 64 : 32;
+    if (!encode_tmap_2d_ex(&to, out, out_dtype, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
+                           static_cast<uint64_t>(N) * out_elem, cw, 32, 128))
+      return;
+    if (residual && !encode_tmap_2d_ex(&tr, residual, dtype, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
+                                       static_cast<uint64_t>(N) * 2, cw, 32, cw == 64 ? 128 : 64))
+      return;
+  }
   p.num_m_blocks = static_cast<int>((M + gemm::BM - 1) / gemm::BM);
   p.num_n_blocks = static_cast<int>((N + gemm::BN - 1) / gemm::BN);
   p.err = err;
+#ifdef MDC_GEMM_TRACE
+  p.trace = g_gemm_trace;
+  p.dbg_mode = g_gemm_dbg_mode;
+#endif
   const int64_t tiles = static_cast<int64_t>(p.num_m_blocks) * p.num_n_blocks;
   if (tiles > 0x7fffffff) { fail("mgpuMatmulEx16: too many tiles"); return; }
   const int grid = static_cast<int>(tiles < di.sms ? tiles : di.sms);
   cudaStream_t s = as_stream(stream);
 
   if (dtype == MGPU_DTYPE_F16) {
-    if (out_dtype == MGPU_DTYPE_F16) launch_gemm_act<__half, __half>(ta, tb, p, grid, act, s);
-    else if (out_dtype == MGPU_DTYPE_F32) launch_gemm_act<__half, float>(ta, tb, p, grid, act, s);
+    if (out_dtype == MGPU_DTYPE_F16) launch_gemm_act<__half, __half>(ta, tb, to, tr, p, grid, act, s);
+    else if (out_dtype == MGPU_DTYPE_F32) launch_gemm_act<__half, float>(ta, tb, to, tr, p, grid, act, s);
     else fail("mgpuMatmulEx16: output type must be the operand type or F32");
   } else {
-    if (out_dtype == MGPU_DTYPE_BF16) launch_gemm_act<__nv_bfloat16, __nv_bfloat16>(ta, tb, p, grid, act, s);
-    else if (out_dtype == MGPU_DTYPE_F32) launch_gemm_act<__nv_bfloat16, float>(ta, tb, p, grid, act, s);
+    if (out_dtype == MGPU_DTYPE_BF16) launch_gemm_act<__nv_bfloat16, __nv_bfloat16>(ta, tb, to, tr, p, grid, act, s);
+    else if (out_dtype == MGPU_DTYPE_F32) launch_gemm_act<__nv_bfloat16, float>(ta, tb, to, tr, p, grid, act, s);
     else fail("mgpuMatmulEx16: output type must be the operand type or F32");
   }
 }
+
+#ifdef MDC_GEMM_TRACE
+MDC_API void mgpuDebugSetGemmTrace(unsigned long long *buf) { g_gemm_trace = buf; }
+MDC_API void mgpuDebugSetGemmMode(int mode) { g_gemm_dbg_mode = mode; }
+#endif
 
 MDC_API uint32_t mgpuOpsCheckDeviceStatus(void *stream) {
   uint32_t *err = device_error_slot();
