@@ -42,9 +42,11 @@ METRIC, UNIT = "encoder_stack_seqs_per_sec", "seq/s"
 T = B_PER_GPU * S
 GEMM_FLOPS_PER_STEP = L * 2 * T * (D * 3 * D + D * D + 2 * D * F)
 GEMM_LAUNCHES_PER_STEP = 4 * L
-# DRAM bytes per Gemm launch from the ncu capture summarised in profiles/ (per launch,
-# averaged over the four shapes of a layer); None until a capture exists.
-GEMM_DRAM_TRAFFIC_PER_LAUNCH = None
+# DRAM bytes per Gemm launch (read + write), averaged over the four Gemms of a layer.  The
+# ncu captures (profiles/gemm_tcgen05_8192tok.md, 8192 tokens) show reads equal to the
+# operand bytes; scaled to the 32768 tokens of a step (A, residual and output grow with the
+# tokens, W does not) that is 117 MB read + 113 MB written.
+GEMM_DRAM_TRAFFIC_PER_LAUNCH = 230.0e6
 
 
 def peaks():
@@ -81,7 +83,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -230,6 +232,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--chunks", type=int, default=4, help="pipeline depth of the host-buffer (e2e) path")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only-timed", action="store_true",
+                    help="stop after the device-resident timed region (used for the ncu launch list)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -270,6 +274,8 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()  # nvidia-smi needs a moment before its first sample; runs until the timed region ends
     layers = make_weights()
     stack = mdc.EncoderStack(layers, H, norm_first=False, causal=False, act=mdc.ACT_GELU_ERF, dtype=mdc.F16)
     x = np.random.default_rng(1 + rank).standard_normal((B_PER_GPU, S, D)).astype(np.float32)
@@ -285,8 +291,6 @@ def main():
     for _ in range(args.warmup):
         step()
     rt.mgpuStreamSynchronize(stream)
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     barrier()
     launches0 = ops.mgpuOpsLaunchCount()
     rt.mgpuEventRecord(ev0, stream)
@@ -304,6 +308,13 @@ def main():
         raise mdc.MdcError(f"device status 0x{status:08x}")
     ms_per_step = ms_total / args.steps
     value = world * B_PER_GPU * args.steps / (ms_total / 1e3)
+    if args.only_timed:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                              "warmup": args.warmup, "ms_per_step": ms_per_step, "gpu_launches": int(launches),
+                              "note": "timed region only"}), flush=True)
+        stack.close()
+        return
 
     # ---------------- per-kernel pass: Gemm launch durations ----------------
     ms_cat = (mdc.C.c_double * 4)()
