@@ -163,6 +163,18 @@ void mgpuTransformerEncoderLayer(const float *input, const float *qkv_weight, co
                                  int64_t head_num, bool norm_first, bool causal, int32_t act,
                                  int32_t dtype, float eps, mgpu_cuda_stream_t stream);
 
+/* No counterpart in the reference.  mgpuMatmul for callers that must not allocate device
+ * memory (a serving loop that cannot take the device-wide synchronisation of cudaMalloc, or
+ * a process whose device memory is already fully reserved by another component): same
+ * arguments and result as mgpuMatmul, but the two 16-bit operand copies live in a fixed
+ * 16 MiB device array inside the library instead of pool memory, and no allocation call of
+ * any kind is made.  Accepts 256 + roundup256(M*Kp*2) + roundup256(N*Kp*2) <= 16 MiB
+ * (Kp = K rounded up to 8); anything larger is rejected with the sticky status set.  The
+ * first call on a device resolves the array's address: make it before any stream capture.
+ * All calls on a device share the array; calls that overlap on the GPU race on it. */
+void mgpuMatmulNoAlloc(float *input, float *weight, float *bias, float *output, int64_t M,
+                       int64_t N, int64_t K, mgpu_cuda_stream_t stream);
+
 /* Number of kernels this library has launched since load (for launch accounting). */
 uint64_t mgpuOpsLaunchCount(void);
 

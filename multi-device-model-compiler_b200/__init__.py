@@ -87,6 +87,7 @@ RUNTIME_SIGNATURES = {
 
 OPS_SIGNATURES = {
     "mgpuMatmul": (None, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
+    "mgpuMatmulNoAlloc": (None, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]),
     "mgpuConv2d": (None, [_vp] * 5 + [_i64] * 17 + [_b, _b, _vp]),
     "mgpuPool2d": (None, [_vp, _vp] + [_i64] * 15 + [_vp]),
     "mgpuLLMDecodingContextLayer": (None, [_vp] * 9 + [_i64] * 5 + [_b, _b, _b, _vp]),

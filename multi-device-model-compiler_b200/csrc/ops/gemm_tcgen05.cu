@@ -607,3 +607,107 @@ MDC_API uint32_t mgpuOpsCheckDeviceStatus(void *stream) {
   }
   return h;
 }
+
+// =========================================================================================
+// mgpuMatmulNoAlloc: mgpuMatmul for callers that must not allocate device memory.
+//
+// mgpuMatmul needs two temporaries (the 16-bit copies of the input and of the transposed
+// weight) and takes them from the runtime's device pool, which calls cudaMalloc whenever the
+// pool has no fitting block.  Some callers cannot afford that call: a serving loop whose
+// latency budget has no room for the device-wide synchronisation cudaMalloc implies, or a
+// process in which another component has reserved all device memory up front so that any
+// further allocation fails.  For them this entry point does the same computation with the
+// temporaries placed in a fixed array that is part of the library image.
+//
+// * The array is kNoAllocScratchBytes (16 MiB) of device memory per GPU that loads the
+//   library, held until the process exits whether the entry point is used or not.
+// * Limit: 256 + roundup256(M * Kp * 2) + roundup256(N * Kp * 2) <= 16 MiB with Kp = K rounded
+//   up to 8 (for example M x N x K = 1024 x 768 x 4096, or 2048 x 512 x 3072).  Larger problems are
+//   rejected with the sticky status set and nothing launched.
+// * The first call on a device looks the array's device address up
+//   (cudaGetSymbolAddress); make that first call before starting any stream capture.
+// * All calls on a device share the one array, which keeps whatever the last call left in
+//   it.  Everything a call reads from it is written by that call first (the padded operand
+//   copies and the status word), but two calls that overlap on the GPU (different streams
+//   without an ordering between them) race on it: order them.
+// * No cudaMalloc / cudaFree / pool call is made on this path.
+// =========================================================================================
+namespace mdc {
+constexpr size_t kNoAllocScratchBytes = size_t(16) << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+// host-side cache of the array's device address, per device ordinal
+static unsigned char *g_noalloc_ptr[64] = {nullptr};
+
+void cast_rows_padded(const float *src, void *dst, int64_t R, int64_t C, int64_t Cp, int32_t dtype,
+                      cudaStream_t s);
+}  // namespace mdc
+
+MDC_API void mgpuMatmulNoAlloc(float *input, float *weight, float *bias, float *output, int64_t M,
+                               int64_t N, int64_t K, void *stream) {
+  if (M <= 0 || N <= 0) return;
+  if (K <= 0) { fail("mgpuMatmulNoAlloc: K must be positive"); return; }
+  const DeviceInfo &di = device_info();
+  if (!di.ok) return;
+  if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff) { fail("mgpuMatmulNoAlloc: shape too large"); return; }
+  const int64_t Kp = (K + 7) / 8 * 8;
+  auto up256 = [](size_t b) { return (b + 255) / 256 * 256; };
+  const size_t a_bytes = up256(static_cast<size_t>(M) * Kp * 2), w_bytes = up256(static_cast<size_t>(N) * Kp * 2);
+  if (256 + a_bytes + w_bytes > kNoAllocScratchBytes) {
+    char msg[200];
+    snprintf(msg, sizeof(msg),
+             "mgpuMatmulNoAlloc: %lld x %lld x %lld needs %zu bytes of scratch, the fixed array holds %zu",
+             (long long)M, (long long)N, (long long)K, 256 + a_bytes + w_bytes, kNoAllocScratchBytes);
+    fail(msg);
+    return;
+  }
+  if (di.device < 0 || di.device >= 64) { fail("mgpuMatmulNoAlloc: device ordinal out of range"); return; }
+  // set-up, once per device, with that device current: the array's name is only a host-side
+  // handle; kernels need the address the runtime resolves for this device
+  if (!g_noalloc_ptr[di.device]) {
+    void *sym = nullptr;
+    if (!check_cuda(cudaGetSymbolAddress(&sym, g_noalloc_scratch), "cudaGetSymbolAddress(scratch)")) return;
+    g_noalloc_ptr[di.device] = static_cast<unsigned char *>(sym);
+  }
+  unsigned char *base = g_noalloc_ptr[di.device];
+  uint32_t *status = reinterpret_cast<uint32_t *>(base);  // first 256 bytes: kernel status word
+  void *a16 = base + 256;
+  void *w16 = base + 256 + a_bytes;
+  cudaStream_t s = as_stream(stream);
+  if (!check_cuda(cudaMemsetAsync(status, 0, 256, s), "cudaMemsetAsync(status)")) return;
+  cast_rows_padded(input, a16, M, K, Kp, MGPU_DTYPE_F16, s);
+  mgpuPackWeight(weight, w16, K, N, MGPU_DTYPE_F16, stream);
+
+  CUtensorMap ta, tb;
+  if (!encode_tmap_2d(&ta, a16, MGPU_DTYPE_F16, static_cast<uint64_t>(Kp), static_cast<uint64_t>(M),
+                      static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BM) ||
+      !encode_tmap_2d(&tb, w16, MGPU_DTYPE_F16, static_cast<uint64_t>(Kp), static_cast<uint64_t>(N),
+                      static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BN))
+    return;
+  GemmParams p;
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(Kp);
+  p.bias = bias;
+  p.residual = nullptr;
+  p.out = output;
+  p.out_vec_ok = (N % 8 == 0) && !(reinterpret_cast<uintptr_t>(output) & 15u);
+  p.bias_vec_ok = bias && !(reinterpret_cast<uintptr_t>(bias) & 15u);
+  p.tma_epi = p.out_vec_ok && (!bias || p.bias_vec_ok);
+  p.num_m_blocks = static_cast<int>((M + gemm::BM - 1) / gemm::BM);
+  p.num_n_blocks = static_cast<int>((N + gemm::BN - 1) / gemm::BN);
+  // the library's own status word if it exists already (so mgpuOpsCheckDeviceStatus sees a
+  // kernel that gave up), else the word at the head of the fixed array
+  p.err = g_err_slot ? g_err_slot : status;
+#ifdef MDC_GEMM_TRACE
+  p.trace = nullptr;
+  p.dbg_mode = 0;
+#endif
+  CUtensorMap to = ta, tr = ta;
+  if (p.tma_epi &&
+      !encode_tmap_2d_ex(&to, output, MGPU_DTYPE_F32, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
+                         static_cast<uint64_t>(N) * 4, 32, 32, 128))
+    return;
+  const int64_t tiles = static_cast<int64_t>(p.num_m_blocks) * p.num_n_blocks;
+  const int grid = static_cast<int>(tiles < di.sms ? tiles : di.sms);
+  launch_gemm_act<__half, float>(ta, tb, to, tr, p, grid, MGPU_ACT_NONE, s);
+}
