@@ -132,6 +132,8 @@ def run_reference(args, rank, world):
     threads, on a bounded sample of the same workload per step."""
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS to 1; the CPU arm is meant to use every host thread
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import oracle
     sample = 16  # sequences per step (the full step is 256 per GPU)
@@ -386,6 +388,7 @@ def main():
     # ---------------- CPU baseline (rank 0, N = 1 only) ----------------
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        os.environ.setdefault("OMP_NUM_THREADS", str(os.cpu_count() or 1))
         oracle = entry.load_oracle()
         sample = 64
         oracle.encoder_stack(x[:1], layers[:1], None, H, round_mode=oracle.ROUND_F16)  # warm the threads

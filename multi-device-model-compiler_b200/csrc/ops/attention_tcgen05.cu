@@ -59,6 +59,36 @@ __device__ __forceinline__ uint32_t pack16<__nv_bfloat16>(float a, float b) {
   return *reinterpret_cast<uint32_t *>(&h);
 }
 
+// One unit of work: 128 queries of one (sequence, head).  Decoded identically by the control
+// thread and the softmax threads, so both walk the same sequence of key tiles.
+struct AttnItem {
+  int q0, head, b, row_base, kv_end, n_kv;
+};
+__device__ __forceinline__ AttnItem attn_item(const AttnParams &p, int item, int q_tiles) {
+  AttnItem it;
+  const int qt = item % q_tiles;
+  const int rest = item / q_tiles;
+  it.head = rest % p.heads;
+  it.b = rest / p.heads;
+  it.q0 = qt * attn::BQ;
+  it.row_base = it.b * p.seq;
+  const int len = p.seq_lens ? min(max(p.seq_lens[it.b], 0), p.seq) : p.seq;
+  it.kv_end = p.causal ? min(len, it.q0 + attn::BQ) : len;  // keys this query tile can see: [0, kv_end)
+  it.n_kv = (it.kv_end + attn::BKV - 1) / attn::BKV;
+  return it;
+}
+
+__device__ __forceinline__ float ex2_fast(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// Persistent: each CTA walks work items item = blockIdx.x, + gridDim.x, ...; the key tiles of
+// all its items form one sequence of steps t = 0, 1, ..., and every barrier completes once
+// per step (parity t & 1), so loads for step t+1 (of the same or of the next item) are issued
+// while step t is still in its softmax: K (and the next item's Q) as soon as S = Q.K^T of
+// step t has been computed, V as soon as P.V of step t has.
 template <typename T16>
 __global__ void __launch_bounds__(attn::THREADS, 2)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnParams p) {
@@ -75,15 +105,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
   uint8_t *sQ = tiles, *sK = tiles + TILE_BYTES, *sV = tiles + 2 * TILE_BYTES, *sP = tiles + 3 * TILE_BYTES;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_tile = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
-  const int q0 = q_tile * BQ;
-  const int len = p.seq_lens ? min(max(p.seq_lens[b], 0), p.seq) : p.seq;
-  // keys this query tile can see: [0, kv_end)
-  int kv_end = len;
-  if (p.causal) kv_end = min(kv_end, q0 + BQ);
-  const int n_kv = (kv_end + BKV - 1) / BKV;
+  const int q_tiles = (p.seq + BQ - 1) / BQ;
+  const int n_items = q_tiles * p.heads * p.batch;
   const int hd = p.heads * D;
-  const int row_base = b * p.seq;  // first token row of this sequence in the packed tensor
 
   if (threadIdx.x == 0) {
     abort_flag_s = 0;
@@ -107,31 +131,51 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
 
   if (warp == 4) {
     // ------------------------------ loads + MMA issue ------------------------------
-    if (lane == 0 && n_kv > 0) {
+    if (lane == 0) {
       constexpr bool kBf16 = std::is_same<T16, __nv_bfloat16>::value;
       constexpr uint32_t idesc_s = make_idesc_f16(BQ, BKV, kBf16, false, false);
       constexpr uint32_t idesc_o = make_idesc_f16(BQ, D, kBf16, false, true);  // V is MN-major
       const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV),
                      p_addr = smem_u32(sP);
-      mbar_arrive_expect_tx(&bar_q, TILE_BYTES);
-      tma_load_2d(sQ, &tmap_qkv, &bar_q, head * D, row_base + q0);
-      mbar_arrive_expect_tx(&bar_k, TILE_BYTES);
-      tma_load_2d(sK, &tmap_qkv, &bar_k, hd + head * D, row_base);
-      mbar_arrive_expect_tx(&bar_v, TILE_BYTES);
-      tma_load_2d(sV, &tmap_qkv, &bar_v, 2 * hd + head * D, row_base);
-      uint32_t code = 0;
-      if (!mbar_wait(&bar_q, 0, abort_flag)) code = 0x51000000u;
-      for (int j = 0; j < n_kv && !code; ++j) {
-        const uint32_t ph = j & 1;
-        if (j > 0) {
-          // S columns are free once the softmax warps have consumed tile j-1 (they arrived
-          // on bar_p_ready, which this thread already waited for); V of tile j can be
-          // fetched once the previous P.V has finished reading the V and P buffers.
-          if (!mbar_wait(&bar_o_full, ph ^ 1, abort_flag)) { code = 0x52000000u | j; break; }
-          mbar_arrive_expect_tx(&bar_v, TILE_BYTES);
-          tma_load_2d(sV, &tmap_qkv, &bar_v, 2 * hd + head * D, row_base + j * BKV);
+      auto load_q = [&](const AttnItem &it) {
+        mbar_arrive_expect_tx(&bar_q, TILE_BYTES);
+        tma_load_2d(sQ, &tmap_qkv, &bar_q, it.head * D, it.row_base + it.q0);
+      };
+      auto load_k = [&](const AttnItem &it, int j) {
+        mbar_arrive_expect_tx(&bar_k, TILE_BYTES);
+        tma_load_2d(sK, &tmap_qkv, &bar_k, hd + it.head * D, it.row_base + j * BKV);
+      };
+      auto load_v = [&](const AttnItem &it, int j) {
+        mbar_arrive_expect_tx(&bar_v, TILE_BYTES);
+        tma_load_2d(sV, &tmap_qkv, &bar_v, 2 * hd + it.head * D, it.row_base + j * BKV);
+      };
+      // first item with at least one visible key
+      int item = blockIdx.x;
+      AttnItem cur{};
+      while (item < n_items && (cur = attn_item(p, item, q_tiles)).n_kv == 0) item += gridDim.x;
+      uint32_t code = 0, t = 0, q_cnt = 0;
+      if (item < n_items) {
+        load_q(cur);
+        load_k(cur, 0);
+        load_v(cur, 0);
+      }
+      int j = 0;
+      while (item < n_items && !code) {
+        const uint32_t ph = t & 1;
+        // the step after this one: next key tile of the item, or tile 0 of the next item
+        int n_item = item, n_j = j + 1;
+        AttnItem nxt = cur;
+        if (n_j >= cur.n_kv) {
+          n_j = 0;
+          n_item = item + gridDim.x;
+          while (n_item < n_items && (nxt = attn_item(p, n_item, q_tiles)).n_kv == 0) n_item += gridDim.x;
         }
-        if (!mbar_wait(&bar_k, ph, abort_flag)) { code = 0x53000000u | j; break; }
+        const bool has_next = n_item < n_items;
+        if (j == 0) {
+          if (!mbar_wait(&bar_q, q_cnt & 1, abort_flag)) { code = 0x51000000u; break; }
+          ++q_cnt;
+        }
+        if (!mbar_wait(&bar_k, ph, abort_flag)) { code = 0x53000000u | (t & 0xffff); break; }
         tc_fence_after();
         {
           const uint64_t a_desc = make_smem_desc_sw128(q_addr, 16, 1024);
@@ -141,13 +185,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
             umma_f16_ss(tmem_base + S_COL, a_desc + 2 * k, b_desc + 2 * k, idesc_s, k != 0);
         }
         umma_commit(&bar_s_full);
-        if (!mbar_wait(&bar_s_full, ph, abort_flag)) { code = 0x54000000u | j; break; }
-        if (j + 1 < n_kv) {  // K buffer is free again: prefetch the next key tile
-          mbar_arrive_expect_tx(&bar_k, TILE_BYTES);
-          tma_load_2d(sK, &tmap_qkv, &bar_k, hd + head * D, row_base + (j + 1) * BKV);
+        if (!mbar_wait(&bar_s_full, ph, abort_flag)) { code = 0x54000000u | (t & 0xffff); break; }
+        if (has_next) {
+          // K (and, when this was the item's last tile, Q) are free: prefetch the next step's
+          if (n_j == 0) load_q(nxt);
+          load_k(nxt, n_j);
         }
-        if (!mbar_wait(&bar_p_ready, ph, abort_flag)) { code = 0x55000000u | j; break; }
-        if (!mbar_wait(&bar_v, ph, abort_flag)) { code = 0x56000000u | j; break; }
+        if (!mbar_wait(&bar_p_ready, ph, abort_flag)) { code = 0x55000000u | (t & 0xffff); break; }
+        if (!mbar_wait(&bar_v, ph, abort_flag)) { code = 0x56000000u | (t & 0xffff); break; }
         tc_fence_after();
         {
 #pragma unroll
@@ -161,129 +206,144 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
           }
         }
         umma_commit(&bar_o_full);
+        if (has_next) {
+          // V and P are free once this P.V has been computed
+          if (!mbar_wait(&bar_o_full, ph, abort_flag)) { code = 0x52000000u | (t & 0xffff); break; }
+          load_v(nxt, n_j);
+        }
+        ++t;
+        item = n_item;
+        j = n_j;
+        cur = nxt;
       }
       if (code) atomicCAS(p.err, 0u, code);
     }
   } else {
     // ------------------------------ softmax + output ------------------------------
     const int r = threadIdx.x;  // query row inside the tile == TMEM lane
-    const int q_local = q0 + r;  // query index inside the sequence
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-    float o_acc[D];
-#pragma unroll
-    for (int e = 0; e < D; ++e) o_acc[e] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+    uint32_t t = 0;  // key tiles processed so far by this CTA (same count as the control thread)
     bool ok = true;
-    for (int j = 0; j < n_kv && ok; ++j) {
-      const uint32_t ph = j & 1;
-      if (!mbar_wait(&bar_s_full, ph, abort_flag)) {
-        atomicCAS(p.err, 0u, 0x61000000u | j);
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      // columns (keys) this row may attend to inside the tile: [0, ncol)
-      int ncol = kv_end - j * BKV;
-      if (p.causal) ncol = min(ncol, q_local + 1 - j * BKV);
-      ncol = max(min(ncol, BKV), 0);
-      // pass 1: row maximum
-      float m_tile = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t s[32];
-        tmem_ld_32x32(tmem_base + lane_addr + S_COL + c * 32, s);
-        tmem_ld_wait();
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const AttnItem it = attn_item(p, item, q_tiles);
+      const int q_local = it.q0 + r;  // query index inside the sequence
+      float o_acc[D];
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c * 32 + i < ncol) m_tile = fmaxf(m_tile, __uint_as_float(s[i]));
-      }
-      const float m_new = fmaxf(m_run, m_tile);
-      // rows with no visible key yet keep m = -inf; use 0 as the reference point then
-      const float m_ref = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = m_run == -INFINITY ? 0.f : exp2f((m_run - m_ref) * p.scale_log2e);
-      // fold in the previous tile's partial product before P is overwritten
-      if (j > 0) {
-        if (!mbar_wait(&bar_o_full, ph ^ 1, abort_flag)) {
-          atomicCAS(p.err, 0u, 0x62000000u | j);
+      for (int e = 0; e < D; ++e) o_acc[e] = 0.f;
+      float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+      for (int j = 0; j < it.n_kv && ok; ++j, ++t) {
+        const uint32_t ph = t & 1;
+        if (!mbar_wait(&bar_s_full, ph, abort_flag)) {
+          atomicCAS(p.err, 0u, 0x61000000u | (t & 0xffff));
           ok = false;
           break;
         }
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld_32x32(tmem_base + lane_addr + O_COL + c * 32, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha_prev, __uint_as_float(o[i]));
-        }
-      }
-      // pass 2: P = exp2((s - m) * c), row sum, 16-bit P into swizzled shared memory
-      float l_tile = 0.f;
-      const float mc = m_ref * p.scale_log2e;
+        // columns (keys) this row may attend to inside the tile: [0, ncol)
+        int ncol = it.kv_end - j * BKV;
+        if (p.causal) ncol = min(ncol, q_local + 1 - j * BKV);
+        ncol = max(min(ncol, BKV), 0);
+        // pass 1: row maximum
+        float m_tile = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t s[32];
-        tmem_ld_32x32(tmem_base + lane_addr + S_COL + c * 32, s);
-        tmem_ld_wait();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = 0.f, p1 = 0.f;
-          if (c * 32 + i < ncol) p0 = exp2f(fmaf(__uint_as_float(s[i]), p.scale_log2e, -mc));
-          if (c * 32 + i + 1 < ncol) p1 = exp2f(fmaf(__uint_as_float(s[i + 1]), p.scale_log2e, -mc));
-          l_tile += p0 + p1;
-          packed[i >> 1] = pack16<T16>(p0, p1);
-        }
-        // 32 keys = four 16-byte chunks of row r in k-block (c / 2); chunk index is
-        // XOR-swizzled with the row (128-byte swizzle, same pattern TMA writes)
-        uint8_t *blk = sP + (c >> 1) * TILE_BYTES + r * 128;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int chunk = (c & 1) * 4 + q;
-          *reinterpret_cast<uint4 *>(blk + ((chunk ^ (r & 7)) << 4)) =
-              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-        }
-      }
-      l_run = fmaf(l_run, alpha, l_tile);
-      m_run = m_new;
-      alpha_prev = alpha;
-      // P visible to the tensor core (async proxy); S reads of this tile are complete
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(&bar_p_ready);
-    }
-    if (ok && n_kv > 0) {
-      const uint32_t ph = (n_kv - 1) & 1;
-      if (!mbar_wait(&bar_o_full, ph, abort_flag)) {
-        atomicCAS(p.err, 0u, 0x63000000u);
-        ok = false;
-      } else {
-        tc_fence_after();
-        // the last tile's own alpha was already applied to l_run; O needs alpha_prev
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld_32x32(tmem_base + lane_addr + O_COL + c * 32, o);
-          tmem_ld_wait();
+        for (int c = 0; c < BKV / 32; ++c) {
+          uint32_t s[32];
+          tmem_ld_32x32(tmem_base + lane_addr + S_COL + c * 32, s);
+          tmem_ld_wait_regs(s);
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha_prev, __uint_as_float(o[i]));
+            if (c * 32 + i < ncol) m_tile = fmaxf(m_tile, __uint_as_float(s[i]));
+        }
+        const float m_new = fmaxf(m_run, m_tile);
+        // rows with no visible key yet keep m = -inf; use 0 as the reference point then
+        const float m_ref = m_new == -INFINITY ? 0.f : m_new;
+        const float alpha = m_run == -INFINITY ? 0.f : ex2_fast((m_run - m_ref) * p.scale_log2e);
+        // fold in the previous tile's partial product before P is overwritten
+        if (j > 0) {
+          if (!mbar_wait(&bar_o_full, ph ^ 1, abort_flag)) {
+            atomicCAS(p.err, 0u, 0x62000000u | (t & 0xffff));
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(tmem_base + lane_addr + O_COL + c * 32, o);
+            tmem_ld_wait_regs(o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha_prev, __uint_as_float(o[i]));
+          }
+        }
+        // pass 2: P = exp2((s - m) * c), row sum, 16-bit P into swizzled shared memory
+        float l_tile = 0.f;
+        const float mc = m_ref * p.scale_log2e;
+#pragma unroll 1
+        for (int c = 0; c < BKV / 32; ++c) {
+          uint32_t s[32];
+          tmem_ld_32x32(tmem_base + lane_addr + S_COL + c * 32, s);
+          tmem_ld_wait_regs(s);
+          uint32_t packed[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = 0.f, p1 = 0.f;
+            if (c * 32 + i < ncol) p0 = ex2_fast(fmaf(__uint_as_float(s[i]), p.scale_log2e, -mc));
+            if (c * 32 + i + 1 < ncol) p1 = ex2_fast(fmaf(__uint_as_float(s[i + 1]), p.scale_log2e, -mc));
+            l_tile += p0 + p1;
+            packed[i >> 1] = pack16<T16>(p0, p1);
+          }
+          // 32 keys = four 16-byte chunks of row r in k-block (c / 2); chunk index is
+          // XOR-swizzled with the row (128-byte swizzle, same pattern TMA writes)
+          uint8_t *blk = sP + (c >> 1) * TILE_BYTES + r * 128;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int chunk = (c & 1) * 4 + q;
+            *reinterpret_cast<uint4 *>(blk + ((chunk ^ (r & 7)) << 4)) =
+                make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+          }
+        }
+        l_run = fmaf(l_run, alpha, l_tile);
+        m_run = m_new;
+        alpha_prev = alpha;
+        // P visible to the tensor core (async proxy); S reads of this tile are complete
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(&bar_p_ready);
+      }
+      if (ok && it.n_kv > 0) {
+        // the last step of this item was t - 1
+        if (!mbar_wait(&bar_o_full, (t - 1) & 1, abort_flag)) {
+          atomicCAS(p.err, 0u, 0x63000000u);
+          ok = false;
+        } else {
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(tmem_base + lane_addr + O_COL + c * 32, o);
+            tmem_ld_wait_regs(o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha_prev, __uint_as_float(o[i]));
+          }
+          // the O columns may be overwritten by the next step's P.V only after this read:
+          // that MMA is issued after the next bar_p_ready, which this thread has not given yet
+          tc_fence_before();
         }
       }
-    }
-    if (ok && q_local < p.seq) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      T16 *dst = static_cast<T16 *>(p.out) + static_cast<size_t>(row_base + q_local) * hd + head * D;
+      if (ok && q_local < p.seq) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        T16 *dst = static_cast<T16 *>(p.out) + static_cast<size_t>(it.row_base + q_local) * hd + it.head * D;
 #pragma unroll
-      for (int g = 0; g < D / 8; ++g) {
-        uint4 o;
-        o.x = pack16<T16>(o_acc[8 * g + 0] * inv, o_acc[8 * g + 1] * inv);
-        o.y = pack16<T16>(o_acc[8 * g + 2] * inv, o_acc[8 * g + 3] * inv);
-        o.z = pack16<T16>(o_acc[8 * g + 4] * inv, o_acc[8 * g + 5] * inv);
-        o.w = pack16<T16>(o_acc[8 * g + 6] * inv, o_acc[8 * g + 7] * inv);
-        reinterpret_cast<uint4 *>(dst)[g] = o;
+        for (int g = 0; g < D / 8; ++g) {
+          uint4 o;
+          o.x = pack16<T16>(o_acc[8 * g + 0] * inv, o_acc[8 * g + 1] * inv);
+          o.y = pack16<T16>(o_acc[8 * g + 2] * inv, o_acc[8 * g + 3] * inv);
+          o.z = pack16<T16>(o_acc[8 * g + 4] * inv, o_acc[8 * g + 5] * inv);
+          o.w = pack16<T16>(o_acc[8 * g + 6] * inv, o_acc[8 * g + 7] * inv);
+          reinterpret_cast<uint4 *>(dst)[g] = o;
+        }
       }
     }
   }
@@ -336,7 +396,11 @@ MDC_API void mgpuAttention(const void *qkv, const int32_t *seq_lens, void *out, 
   p.causal = causal ? 1 : 0;
   p.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(attn::D));
   p.err = err;
-  dim3 grid(static_cast<unsigned>(q_tiles), static_cast<unsigned>(heads), static_cast<unsigned>(batch));
+  const int64_t n_items = q_tiles * heads * batch;
+  if (n_items > 0x7fffffff) { fail("mgpuAttention: shape too large"); return; }
+  // persistent CTAs, two per SM (80 KiB of shared memory and 256 TMEM columns each)
+  const int64_t slots = static_cast<int64_t>(di.sms) * 2;
+  dim3 grid(static_cast<unsigned>(n_items < slots ? n_items : slots));
   cudaStream_t s = as_stream(stream);
   ProfileScope prof(kCatAttention, s);
   if (dtype == MGPU_DTYPE_F16) {

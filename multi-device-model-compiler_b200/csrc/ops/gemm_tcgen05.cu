@@ -17,8 +17,18 @@
 //            way through a TMA load.  (Shapes whose rows are not 16-byte multiples fall
 //            back to direct stores.)
 // TMEM holds two accumulators (2 x 256 columns) so the epilogue of tile i overlaps the
-// mainloop of tile i+1.  No cluster launch and no multicast: every CTA fetches its own tiles
-// and relies on L2 for reuse.  All waits are bounded (see ptx_sm100.cuh).
+// mainloop of tile i+1.  Every CTA fetches its own tiles with plain TMA loads and relies on
+// L2 for reuse.  All waits are bounded (see ptx_sm100.cuh).
+//
+// Two variants of the same kernel (template parameter CG):
+//   CG = 1  one CTA per 128 x 256 tile (small problems).
+//   CG = 2  CTA pairs (cluster of 2, tcgen05 cta_group::2) on 256 x 256 tiles: each CTA
+//           stages its 128 rows of A and HALF of the W rows (32 KiB per k-block instead of
+//           48), the leader CTA issues one M = 256 MMA for the pair, each CTA keeps its own
+//           128 x 256 accumulator and runs its own epilogue.  Tensor-core operand reads and
+//           TMA writes compete for shared-memory bandwidth; halving the W bytes per SM is
+//           what lifts the mainloop, and the smaller stage allows a 5-deep ring.
+#include <cstdlib>
 #include <type_traits>
 
 #include "activation.cuh"
@@ -29,16 +39,24 @@ namespace mdc {
 
 namespace gemm {
 constexpr int BM = 128, BN = 256, BK = 64;
-constexpr int STAGES = 3;
 constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 64 + EPI_WARPS * 32;
 constexpr int TMEM_COLS = 512;
 constexpr int EPI_BUF_BYTES = 4096;  // 32 rows x 128 bytes, per warp, one for output and one for residual
-constexpr size_t SMEM_BYTES =
-    static_cast<size_t>(STAGES) * STAGE_BYTES + EPI_WARPS * 2 * EPI_BUF_BYTES + 1024;  // + alignment slack
+template <int CG>
+struct Cfg {
+  static constexpr int B_ROWS = BN / CG;            // W rows this CTA stages per k-block
+  static constexpr int B_BYTES = B_ROWS * BK * 2;   // 32 KiB (CG 1) / 16 KiB (CG 2)
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = CG == 2 ? 4 : 3;
+  // per epilogue warp: output staging (two buffers for pairs, so a chunk does not wait for
+  // the previous chunk's TMA store to drain) + one residual buffer
+  static constexpr int OUT_BUFS = CG == 2 ? 2 : 1;
+  static constexpr int EPI_WARP_BYTES = (OUT_BUFS + 1) * EPI_BUF_BYTES;
+  static constexpr size_t SMEM_BYTES =
+      static_cast<size_t>(STAGES) * STAGE_BYTES + EPI_WARPS * EPI_WARP_BYTES + 1024;  // + alignment slack
+};
 }  // namespace gemm
 
 struct GemmParams {
@@ -50,10 +68,10 @@ struct GemmParams {
   int out_vec_ok;   // rows of out / residual can be accessed with 16-byte vectors
   int bias_vec_ok;  // bias is 16-byte aligned
   int num_m_blocks, num_n_blocks;
+  int cta_group;  // 1: one CTA per 128 x 256 tile; 2: CTA pairs on 256 x 256 tiles
   uint32_t *err;
 #ifdef MDC_GEMM_TRACE
   unsigned long long *trace;  // [grid][8] cycle counters (debug builds only)
-  int dbg_mode;               // 1: loads only (no MMA issued); 2: MMA only (no loads issued)
 #endif
 };
 
@@ -114,24 +132,35 @@ __device__ __forceinline__ void load_res8(const __nv_bfloat16 *src, float *v) {
 // erf(x) = 1 - (a1 t + ... + a5 t^5) exp(-x^2), t = 1/(1 + p x) (Abramowitz & Stegun 7.1.26,
 // |error| <= 1.5e-7), a third of the instructions of erff(): the epilogue runs beside the
 // tensor pipe and must keep up with it, and the result is rounded to 16 bits anyway.
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
 template <int ACT>
 __device__ __forceinline__ float act_fast(float v) {
   if constexpr (ACT == kActGeluErf) {
-    const float x = fabsf(v) * 0.70710678118654752440f;
-    const float t = __fdividef(1.0f, fmaf(0.3275911f, x, 1.0f));
+    // y = |v| / sqrt(2) * sqrt(log2 e), so that exp(-x^2) = 2^(-y^2); p rescaled to match
+    const float y = fabsf(v) * 0.84932180028f;
+    const float t = rcp_approx(fmaf(0.27273750f, y, 1.0f));
     float poly = fmaf(1.061405429f, t, -1.453152027f);
     poly = fmaf(poly, t, 1.421413741f);
     poly = fmaf(poly, t, -0.284496736f);
     poly = fmaf(poly, t, 0.254829592f);
-    const float erf_abs = fmaf(-poly * t, __expf(-x * x), 1.0f);
+    const float erf_abs = fmaf(-poly * t, ex2_approx(-y * y), 1.0f);
     const float h = 0.5f * v;
-    return fmaf(fabsf(h), erf_abs, h);  // 0.5 v (1 + sign(v) erf|x|)
+    return fmaf(fabsf(h), erf_abs, h);  // 0.5 v (1 + sign(v) erf(|v| / sqrt 2))
   } else {
     return act_apply_t<ACT>(v);
   }
 }
 
-template <typename T16, typename TOut, int ACT>
+template <typename T16, typename TOut, int ACT, int CG>
 __global__ void __launch_bounds__(gemm::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
@@ -139,6 +168,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_res, const GemmParams p) {
   using namespace gemm;
   using namespace ptx;
+  using C = Cfg<CG>;
+  constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES;
   extern __shared__ uint8_t smem_dyn[];
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
   __shared__ uint64_t res_bar[EPI_WARPS];
@@ -150,7 +181,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+#ifdef MDC_GEMM_TRACE
+  const unsigned long long trace_c0 = clock64(), trace_t0 = ptx::globaltimer_ns();
+#endif
+  // CG == 2: the two CTAs of a cluster work on one 256-row tile; rank 0 leads
+  const int cta_rank = CG == 2 ? static_cast<int>(cluster_ctarank()) : 0;
+  const bool leader = cta_rank == 0;
+  const int worker = static_cast<int>(blockIdx.x) / CG, num_workers = static_cast<int>(gridDim.x) / CG;
+  // tiles are counted in units of (CG * 128) rows x 256 columns
+  const int num_m_units = (p.num_m_blocks + CG - 1) / CG;
+  const int num_tiles = num_m_units * p.num_n_blocks;
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -158,22 +198,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+      mbar_init(&full_bar[s], 1);   // the leader's arrive.expect_tx (covers both CTAs' bytes)
+      mbar_init(&empty_bar[s], 1);  // one tcgen05.commit
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full_bar[a], 1);
-      mbar_init(&acc_empty_bar[a], EPI_WARPS * 32);
+      mbar_init(&acc_empty_bar[a], CG * EPI_WARPS * 32);  // epilogue threads of the whole pair
     }
     for (int w = 0; w < EPI_WARPS; ++w) mbar_init(&res_bar[w], 1);
     mbar_init_fence();
   }
   if (warp == 1) {
-    tmem_alloc(&tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (CG == 2) {
+      tmem_alloc_cg2(&tmem_slot, TMEM_COLS);
+      tmem_relinquish_cg2();
+    } else {
+      tmem_alloc(&tmem_slot, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();  // the peer's barriers exist before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
 
@@ -183,8 +229,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        const int m_blk = tile % p.num_m_blocks, n_blk = tile / p.num_m_blocks;
+      for (int tile = worker; ok && tile < num_tiles; tile += num_workers) {
+        const int m_blk = (tile % num_m_units) * CG + cta_rank, n_blk = tile / num_m_units;
         for (int kb = 0; kb < num_kb; ++kb) {
           { TRACE_T0();
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
@@ -195,29 +241,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           TRACE_ADD(0); }
           uint8_t *sa = tiles + stage * STAGE_BYTES;
           uint8_t *sb = sa + A_BYTES;
-#ifdef MDC_GEMM_TRACE
-          if (p.dbg_mode == 2) { mbar_arrive(&full_bar[stage]); } else
-#endif
-          {
-          mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
-          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m_blk * BM);
-          tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n_blk * BN);
+          if constexpr (CG == 2) {
+            // both CTAs' copies complete on the LEADER's barrier, which expects the bytes of both
+            const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);
+            if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+            tma_load_2d_cg2(sa, &tmap_a, bar, kb * BK, m_blk * BM);
+            tma_load_2d_cg2(sb, &tmap_b, bar, kb * BK, n_blk * BN + cta_rank * C::B_ROWS);
+          } else {
+            mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m_blk * BM);
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n_blk * BN);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc =
-          make_idesc_f16(BM, BN, sizeof(T16) == 2 && std::is_same<T16, __nv_bfloat16>::value, false, false);
+    // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_f16(BM * CG, BN, std::is_same<T16, __nv_bfloat16>::value, false, false);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      for (int tile = worker; ok && tile < num_tiles; tile += num_workers) {
         { TRACE_T0();
         if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
           atomicCAS(p.err, 0u, 0x30000000u | static_cast<uint32_t>(acc));
@@ -238,20 +286,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
           const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
           const uint64_t b_desc = make_smem_desc_sw128(sa + A_BYTES, 16, 1024);
-#ifdef MDC_GEMM_TRACE
-          if (p.dbg_mode != 1)
-#endif
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // 16 k-elements = 32 bytes further along the 128-byte swizzled row
-            umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * k),
-                        b_desc + static_cast<uint64_t>(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (CG == 2)
+              umma_f16_ss_cg2(d_tmem, a_desc + static_cast<uint64_t>(2 * k),
+                              b_desc + static_cast<uint64_t>(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * k),
+                          b_desc + static_cast<uint64_t>(2 * k), idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
+          // the stage is reusable (in both CTAs) once these MMAs have read it
+          if constexpr (CG == 2) {
+            umma_commit_cg2(smem_u32(&empty_bar[stage]));
+            umma_commit_cg2(mapa_u32(smem_u32(&empty_bar[stage]), 1));
+          } else {
+            umma_commit(&empty_bar[stage]);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        umma_commit(&acc_full_bar[acc]);  // accumulator complete
+        // accumulator complete: wake the epilogue warps of both CTAs
+        if constexpr (CG == 2) {
+          umma_commit_cg2(smem_u32(&acc_full_bar[acc]));
+          umma_commit_cg2(mapa_u32(smem_u32(&acc_full_bar[acc]), 1));
+        } else {
+          umma_commit(&acc_full_bar[acc]);
+        }
         if ((acc ^= 1) == 0) acc_phase ^= 1;
       }
     }
@@ -262,13 +323,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int half_sel = ew >> 2;   // which 128 accumulator columns this warp handles
     TOut *out = static_cast<TOut *>(p.out);
     const T16 *res = static_cast<const T16 *>(p.residual);
-    uint8_t *my_out = tiles + STAGES * STAGE_BYTES + ew * 2 * EPI_BUF_BYTES;
-    uint8_t *my_res = my_out + EPI_BUF_BYTES;
+    uint8_t *my_out_base = tiles + STAGES * STAGE_BYTES + ew * C::EPI_WARP_BYTES;
+    uint8_t *my_res = my_out_base + C::OUT_BUFS * EPI_BUF_BYTES;
+    int out_buf = 0;
     uint32_t res_phase = 0;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int m_blk = tile % p.num_m_blocks, n_blk = tile / p.num_m_blocks;
+    // the accumulator is handed back to the leader's MMA thread, in whichever CTA it lives
+    const uint32_t acc_empty_addr0 = mapa_u32(smem_u32(&acc_empty_bar[0]), 0);
+    const uint32_t acc_empty_addr1 = mapa_u32(smem_u32(&acc_empty_bar[1]), 0);
+    for (int tile = worker; tile < num_tiles; tile += num_workers) {
+      const int m_blk = (tile % num_m_units) * CG + cta_rank, n_blk = tile / num_m_units;
       { TRACE_T0();
       if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag)) {
         atomicCAS(p.err, 0u, 0x40000000u | static_cast<uint32_t>(acc));
@@ -278,84 +343,95 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_after();
       TRACE_T0();
       if (p.tma_epi) {
-        // ---- staged path: 32 rows x CW columns (128 bytes of output per row) at a time ----
-        constexpr int CW = sizeof(TOut) == 2 ? 64 : 32;
-        constexpr int RES_ROW_BYTES = CW * 2;  // residual is 16-bit
+        // ---- staged path.  The warp owns 32 rows x 128 accumulator columns, read from TMEM in
+        // four 32-column pieces; the load of the next piece is in flight while this one goes
+        // through bias / activation / residual.  Output leaves in chunks of CW columns
+        // (128 bytes per row): swizzled staging buffer -> one TMA store. ----
+        constexpr int CW = sizeof(TOut) == 2 ? 64 : 32;   // columns per staged chunk
+        constexpr int SUBS = CW / 32;                      // 32-column pieces per chunk
+        constexpr int RES_ROW_BYTES = CW * 2;              // residual is 16-bit
         const int row0 = m_blk * BM + quarter * 32;
-        const uint32_t lane_base = tmem_base + static_cast<uint32_t>(acc * BN) +
-                                   (static_cast<uint32_t>(quarter * 32) << 16);
+        const int gcol_base = n_blk * BN + half_sel * (BN / 2);
+        const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * BN + half_sel * (BN / 2)) +
+                                (static_cast<uint32_t>(quarter * 32) << 16);
+        // pieces that hold real columns (uniform across the warp; N is a multiple of 4 here)
+        const int n_sub = gcol_base >= p.N ? 0 : min(4, (p.N - gcol_base + 31) / 32);
+        uint32_t raw[32];
+        if (n_sub > 0) tmem_ld_32x32(t_base, raw);
         bool chunk_ok = true;
+        uint8_t *my_out = my_out_base;
 #pragma unroll 1
-        for (int chunk = 0; chunk < BN / 2 / CW && chunk_ok; ++chunk) {
-          const int col0 = half_sel * (BN / 2) + chunk * CW;
-          const int gcol0 = n_blk * BN + col0;
-          if (gcol0 >= p.N) break;  // uniform across the warp
-          if (res && lane == 0) {
-            mbar_arrive_expect_tx(&res_bar[ew], 32 * RES_ROW_BYTES);
-            tma_load_2d(my_res, &tmap_res, &res_bar[ew], gcol0, row0);
-          }
-          float v[CW];
-          {
-            uint32_t r[32];
-            tmem_ld_32x32(lane_base + col0, r);
-            if constexpr (CW == 64) {
-              uint32_t r2[32];
-              tmem_ld_32x32(lane_base + col0 + 32, r2);
-              tmem_ld_wait();
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[32 + j] = __uint_as_float(r2[j]);
-            } else {
-              tmem_ld_wait();
+        for (int sub = 0; sub < n_sub; ++sub) {
+          const int gcol = gcol_base + sub * 32;
+          const int sub_in_chunk = sub % SUBS;
+          const int gcol_chunk = gcol - sub_in_chunk * 32;
+          if (sub_in_chunk == 0) {
+            if (res && lane == 0) {
+              mbar_arrive_expect_tx(&res_bar[ew], 32 * RES_ROW_BYTES);
+              tma_load_2d(my_res, &tmap_res, &res_bar[ew], gcol_chunk, row0);
             }
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            // the TMA store that last used this staging buffer must have finished reading it
+            my_out = my_out_base + out_buf * EPI_BUF_BYTES;
+            if (lane == 0) tma_store_wait_read<C::OUT_BUFS - 1>();
+            __syncwarp();
+            if constexpr (C::OUT_BUFS == 2) out_buf ^= 1;
           }
+          tmem_ld_wait_regs(raw);
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+          if (sub + 1 < n_sub) tmem_ld_32x32(t_base + (sub + 1) * 32, raw);  // overlaps the math below
           if (p.bias) {
 #pragma unroll
-            for (int j = 0; j < CW; j += 4) {
-              if (gcol0 + j < p.N) {  // N is a multiple of 4 on this path
-                const float4 b = __ldg(reinterpret_cast<const float4 *>(p.bias + gcol0 + j));
+            for (int j = 0; j < 32; j += 4) {
+              if (gcol + j < p.N) {
+                const float4 b = __ldg(reinterpret_cast<const float4 *>(p.bias + gcol + j));
                 v[j] += b.x; v[j + 1] += b.y; v[j + 2] += b.z; v[j + 3] += b.w;
               }
             }
           }
 #pragma unroll
-          for (int j = 0; j < CW; ++j) v[j] = act_fast<ACT>(v[j]);
+          for (int j = 0; j < 32; ++j) v[j] = act_fast<ACT>(v[j]);
           if (res) {
-            if (!mbar_wait(&res_bar[ew], res_phase, abort_flag)) {
-              atomicCAS(p.err, 0u, 0x50000000u | static_cast<uint32_t>(ew));
-              chunk_ok = false;
-              break;
+            if (sub_in_chunk == 0) {
+              if (!mbar_wait(&res_bar[ew], res_phase, abort_flag)) {
+                atomicCAS(p.err, 0u, 0x50000000u | static_cast<uint32_t>(ew));
+                chunk_ok = false;
+                break;
+              }
+              res_phase ^= 1;
             }
-            res_phase ^= 1;
-            // residual rows are RES_ROW_BYTES long; 16-byte pieces are XOR-swizzled like TMA wrote them
+            // this piece is 64 bytes (four 16-byte pieces) of the residual row; the pieces are
+            // XOR-swizzled the way TMA wrote them (128-byte rows: ^ row%8; 64-byte rows: ^ (row/2)%4)
 #pragma unroll
-            for (int j = 0; j < RES_ROW_BYTES / 16; ++j) {
-              const int phys = RES_ROW_BYTES == 128 ? (j ^ (lane & 7)) : (j ^ ((lane >> 1) & 3));
+            for (int j = 0; j < 4; ++j) {
+              const int piece = sub_in_chunk * 4 + j;
+              const int phys = RES_ROW_BYTES == 128 ? (piece ^ (lane & 7)) : (piece ^ ((lane >> 1) & 3));
               float rv[8];
               load_res8(reinterpret_cast<const T16 *>(my_res + lane * RES_ROW_BYTES + (phys << 4)), rv);
 #pragma unroll
               for (int e = 0; e < 8; ++e) v[8 * j + e] += rv[e];
             }
           }
-          // the previous TMA store must have finished reading the staging buffer
-          if (lane == 0) tma_store_wait_read<0>();
-          __syncwarp();
-          constexpr int EPC = 16 / sizeof(TOut);  // elements per 16-byte piece
+          if constexpr (sizeof(TOut) == 2) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            uint8_t *dst = my_out + lane * 128 + ((j ^ (lane & 7)) << 4);
-            if constexpr (sizeof(TOut) == 2) {
-              store_out8<TOut>(reinterpret_cast<TOut *>(dst), v + EPC * j);
-            } else {
-              *reinterpret_cast<float4 *>(dst) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            for (int j = 0; j < 4; ++j) {  // 32 columns = four 16-byte pieces of the 128-byte row
+              const int piece = sub_in_chunk * 4 + j;
+              store_out8<TOut>(reinterpret_cast<TOut *>(my_out + lane * 128 + ((piece ^ (lane & 7)) << 4)), v + 8 * j);
             }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<float4 *>(my_out + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                  make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
           }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&tmap_out, my_out, gcol0, row0);  // rows / columns past M / N are clipped
-            tma_store_commit();
+          if (sub_in_chunk == SUBS - 1 || sub + 1 == n_sub) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_out, my_out, gcol_chunk, row0);  // rows / columns past M / N are clipped
+              tma_store_commit();
+            }
           }
         }
         if (!chunk_ok) break;
@@ -420,14 +496,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       }
       tc_fence_before();
-      mbar_arrive(&acc_empty_bar[acc]);
+      if constexpr (CG == 2) mbar_arrive_cluster(acc ? acc_empty_addr1 : acc_empty_addr0);
+      else mbar_arrive(&acc_empty_bar[acc]);
       if (threadIdx.x == 64) { TRACE_ADD(4); }
       if ((acc ^= 1) == 0) acc_phase ^= 1;
     }
     if (lane == 0) tma_store_wait<0>();  // all staged output has left shared memory
   }
 #ifdef MDC_GEMM_TRACE
-  if (threadIdx.x == 0 && p.trace) p.trace[blockIdx.x * 8 + 7] = (unsigned long long)clock64();
+  if (threadIdx.x == 0 && p.trace) {
+    p.trace[blockIdx.x * 8 + 5] = (unsigned long long)clock64() - trace_c0;       // SM cycles in the kernel
+    p.trace[blockIdx.x * 8 + 6] = ptx::globaltimer_ns() - trace_t0;               // nanoseconds in the kernel
+  }
 #endif
 
   // ------------------------------ teardown ------------------------------
@@ -439,14 +519,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
   tc_fence_before();
   __syncthreads();
+  // neither CTA of a pair may retire (or free tensor memory) while the other can still
+  // signal its barriers or read its shared memory
+  if constexpr (CG == 2) cluster_sync_all();
   tc_fence_after();
-  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (warp == 1) {
+    if constexpr (CG == 2) tmem_dealloc_cg2(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
+  }
 }
 
 // ---------------------------------------------------------------------------------------
 #ifdef MDC_GEMM_TRACE
 static unsigned long long *g_gemm_trace = nullptr;
-static int g_gemm_dbg_mode = 0;
 #endif
 static uint32_t *g_err_slot = nullptr;
 
@@ -481,23 +566,47 @@ bool encode_tmap_2d(CUtensorMap *map, const void *base, int32_t dtype, uint64_t 
   return encode_tmap_2d_ex(map, base, dtype, inner, outer, row_stride_bytes, box_inner, box_outer, 128);
 }
 
-template <typename T16, typename TOut, int ACT>
-static void launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to,
-                        const CUtensorMap &tr, const GemmParams &p, int grid, cudaStream_t s) {
-  auto kern = gemm_tcgen05_kernel<T16, TOut, ACT>;
+template <typename T16, typename TOut, int ACT, int CG>
+static void launch_gemm_cg(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to,
+                           const CUtensorMap &tr, const GemmParams &p, int grid, cudaStream_t s) {
+  auto kern = gemm_tcgen05_kernel<T16, TOut, ACT, CG>;
+  constexpr size_t smem = gemm::Cfg<CG>::SMEM_BYTES;
   static bool attr_set = false;
   if (!attr_set) {
-    if (!check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(gemm::SMEM_BYTES)),
+    if (!check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
                     "cudaFuncSetAttribute(gemm)"))
       return;
     attr_set = true;
   }
   {
     ProfileScope prof(kCatGemm, s);
-    kern<<<grid, gemm::THREADS, gemm::SMEM_BYTES, s>>>(ta, tb, to, tr, p);
+    if constexpr (CG == 2) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(static_cast<unsigned>(grid));
+      cfg.blockDim = dim3(gemm::THREADS);
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = s;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      check_cuda(cudaLaunchKernelEx(&cfg, kern, ta, tb, to, tr, p), "cudaLaunchKernelEx(gemm pair)");
+    } else {
+      kern<<<grid, gemm::THREADS, smem, s>>>(ta, tb, to, tr, p);
+    }
   }
   launched("gemm_tcgen05_kernel");
+}
+
+// p.cta_group selects the variant; grid is CTAs (even for pairs)
+template <typename T16, typename TOut, int ACT>
+static void launch_gemm(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &to,
+                        const CUtensorMap &tr, const GemmParams &p, int grid, cudaStream_t s) {
+  if (p.cta_group == 2) launch_gemm_cg<T16, TOut, ACT, 2>(ta, tb, to, tr, p, grid, s);
+  else launch_gemm_cg<T16, TOut, ACT, 1>(ta, tb, to, tr, p, grid, s);
 }
 
 template <typename T16, typename TOut>
@@ -510,6 +619,26 @@ static void launch_gemm_act(const CUtensorMap &ta, const CUtensorMap &tb, const 
   case MGPU_ACT_GELU_TANH: launch_gemm<T16, TOut, kActGeluTanh>(ta, tb, to, tr, p, grid, s); break;
   default: fail("mgpuMatmulEx16: unknown activation");
   }
+}
+
+// CTA pairs whenever there are at least two 128-row blocks; MDC_GEMM_CTA_GROUP=1|2 overrides
+// (for measurements).
+static int choose_cta_group(int64_t M) {
+  static const int forced = [] {
+    const char *e = getenv("MDC_GEMM_CTA_GROUP");
+    return e ? atoi(e) : 0;
+  }();
+  if (forced == 1 || forced == 2) return forced;
+  return M > gemm::BM ? 2 : 1;
+}
+
+// persistent grid: one worker (CTA or CTA pair) per tile up to the number the device holds
+static int gemm_grid(const GemmParams &p, int sms) {
+  const int cg = p.cta_group;
+  const int64_t tiles = static_cast<int64_t>((p.num_m_blocks + cg - 1) / cg) * p.num_n_blocks;
+  if (tiles > 0x7fffffff) return -1;
+  const int64_t max_workers = sms / cg;
+  return static_cast<int>((tiles < max_workers ? tiles : max_workers) * cg);
 }
 
 }  // namespace mdc
@@ -532,14 +661,16 @@ MDC_API void mgpuMatmulEx16(const void *a, const void *w_nk, const float *bias, 
   uint32_t *err = device_error_slot();
   if (!err) return;
 
+  const int cta_group = choose_cta_group(M);
   CUtensorMap ta, tb;
   if (!encode_tmap_2d(&ta, a, dtype, static_cast<uint64_t>(Kp), static_cast<uint64_t>(M),
                       static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BM) ||
       !encode_tmap_2d(&tb, w_nk, dtype, static_cast<uint64_t>(Kp), static_cast<uint64_t>(N),
-                      static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BN))
+                      static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BN / cta_group))
     return;
 
   GemmParams p;
+  p.cta_group = cta_group;
   p.M = static_cast<int>(M);
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(Kp);
@@ -569,11 +700,9 @@ MDC_API void mgpuMatmulEx16(const void *a, const void *w_nk, const float *bias, 
   p.err = err;
 #ifdef MDC_GEMM_TRACE
   p.trace = g_gemm_trace;
-  p.dbg_mode = g_gemm_dbg_mode;
 #endif
-  const int64_t tiles = static_cast<int64_t>(p.num_m_blocks) * p.num_n_blocks;
-  if (tiles > 0x7fffffff) { fail("mgpuMatmulEx16: too many tiles"); return; }
-  const int grid = static_cast<int>(tiles < di.sms ? tiles : di.sms);
+  const int grid = gemm_grid(p, di.sms);
+  if (grid <= 0) { fail("mgpuMatmulEx16: too many tiles"); return; }
   cudaStream_t s = as_stream(stream);
 
   if (dtype == MGPU_DTYPE_F16) {
@@ -589,7 +718,6 @@ MDC_API void mgpuMatmulEx16(const void *a, const void *w_nk, const float *bias, 
 
 #ifdef MDC_GEMM_TRACE
 MDC_API void mgpuDebugSetGemmTrace(unsigned long long *buf) { g_gemm_trace = buf; }
-MDC_API void mgpuDebugSetGemmMode(int mode) { g_gemm_dbg_mode = mode; }
 #endif
 
 MDC_API uint32_t mgpuOpsCheckDeviceStatus(void *stream) {
@@ -677,13 +805,15 @@ MDC_API void mgpuMatmulNoAlloc(float *input, float *weight, float *bias, float *
   cast_rows_padded(input, a16, M, K, Kp, MGPU_DTYPE_F16, s);
   mgpuPackWeight(weight, w16, K, N, MGPU_DTYPE_F16, stream);
 
+  const int cta_group = choose_cta_group(M);
   CUtensorMap ta, tb;
   if (!encode_tmap_2d(&ta, a16, MGPU_DTYPE_F16, static_cast<uint64_t>(Kp), static_cast<uint64_t>(M),
                       static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BM) ||
       !encode_tmap_2d(&tb, w16, MGPU_DTYPE_F16, static_cast<uint64_t>(Kp), static_cast<uint64_t>(N),
-                      static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BN))
+                      static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BN / cta_group))
     return;
   GemmParams p;
+  p.cta_group = cta_group;
   p.M = static_cast<int>(M);
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(Kp);
@@ -700,14 +830,13 @@ MDC_API void mgpuMatmulNoAlloc(float *input, float *weight, float *bias, float *
   p.err = g_err_slot ? g_err_slot : status;
 #ifdef MDC_GEMM_TRACE
   p.trace = nullptr;
-  p.dbg_mode = 0;
 #endif
   CUtensorMap to = ta, tr = ta;
   if (p.tma_epi &&
       !encode_tmap_2d_ex(&to, output, MGPU_DTYPE_F32, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
                          static_cast<uint64_t>(N) * 4, 32, 32, 128))
     return;
-  const int64_t tiles = static_cast<int64_t>(p.num_m_blocks) * p.num_n_blocks;
-  const int grid = static_cast<int>(tiles < di.sms ? tiles : di.sms);
+  const int grid = gemm_grid(p, di.sms);
+  if (grid <= 0) { fail("mgpuMatmulNoAlloc: too many tiles"); return; }
   launch_gemm_act<__half, float>(ta, tb, to, tr, p, grid, MGPU_ACT_NONE, s);
 }
