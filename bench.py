@@ -194,6 +194,12 @@ def run_micro(args):
         out = mdc.DeviceBuffer(Bq * S * H * 64 * 2, stream)
         fn = lambda: ops.mgpuAttention(q.ptr, None, out.ptr, Bq, S, H, 64, False, mdc.F16, stream)
         work, unit = 4.0 * Bq * H * S * S * 64, "TFLOP/s"
+    elif name == "layernorm_f16":
+        rows, n = tokens, args.hidden
+        a = mdc.to_device(rng.standard_normal((rows, n)).astype(np.float16), stream)
+        c = mdc.DeviceBuffer(rows * n * 2, stream)
+        fn = lambda: ops.mgpuLayerNormEx(a.ptr, None, None, None, None, c.ptr, 1e-5, rows, n, mdc.F16, mdc.F16, stream)
+        work, unit = 2.0 * rows * n * 2, "GB/s"
     elif name in ("layernorm_f32", "add_f32"):
         rows, n = tokens, args.hidden
         a = mdc.to_device(rng.standard_normal((rows, n)).astype(np.float32), stream)
@@ -225,7 +231,7 @@ def run_micro(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--micro", default=None, help="run one kernel only (for profiling): " + ", ".join(
-        list(MICRO) + ["attention", "layernorm_f32", "add_f32"]))
+        list(MICRO) + ["attention", "layernorm_f32", "layernorm_f16", "add_f32"]))
     ap.add_argument("--tokens", type=int, default=8192, help="--micro: rows / tokens of the small case")
     ap.add_argument("--hidden", type=int, default=768, help="--micro layernorm_f32 / add_f32: row length")
     ap.add_argument("--gpus", type=int, default=1)

@@ -185,6 +185,9 @@ uint64_t mgpuOpsLaunchCount(void);
  * Not to be left on in production: the events add a little work between kernels. */
 void mgpuOpsProfileBegin(void);
 void mgpuOpsProfileEnd(double *ms_per_category, uint64_t *launches_per_category);
+/* Alternative to mgpuOpsProfileEnd: every launch on its own, in launch order (category and
+ * milliseconds); returns how many were written (at most capacity). */
+int64_t mgpuOpsProfileEndSpans(int32_t *category, float *ms, int64_t capacity);
 
 /* The tensor-core kernels bound every wait on a barrier; a kernel that gives up writes a
  * code into a device status word instead of hanging.  This call synchronises `stream`,

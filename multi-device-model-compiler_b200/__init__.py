@@ -112,6 +112,7 @@ OPS_SIGNATURES = {
     "mgpuOpsCheckDeviceStatus": (_u32, [_vp]),
     "mgpuOpsProfileBegin": (None, []),
     "mgpuOpsProfileEnd": (None, [C.POINTER(C.c_double), C.POINTER(_u64)]),
+    "mgpuOpsProfileEndSpans": (_i64, [C.POINTER(_i32), C.POINTER(_f), _i64]),
 }
 
 _rt = None

@@ -191,6 +191,29 @@ MDC_API void mgpuOpsProfileBegin(void) {
   g_profiling = true;
 }
 
+// Like mgpuOpsProfileEnd, but returns every launch separately, in launch order: its
+// category and its device time.  Returns the number of launches written (at most `capacity`).
+MDC_API int64_t mgpuOpsProfileEndSpans(int32_t *category, float *ms, int64_t capacity) {
+  g_profiling = false;
+  int64_t n = 0;
+  for (ProfileSpan &sp : g_spans) {
+    float t = 0.f;
+    if (cudaEventSynchronize(sp.end) == cudaSuccess && cudaEventElapsedTime(&t, sp.begin, sp.end) == cudaSuccess) {
+      if (n < capacity) {
+        if (category) category[n] = sp.cat;
+        if (ms) ms[n] = t;
+        ++n;
+      }
+    } else {
+      (void)cudaGetLastError();
+    }
+    g_spare_events.push_back(sp.begin);
+    g_spare_events.push_back(sp.end);
+  }
+  g_spans.clear();
+  return n;
+}
+
 MDC_API void mgpuOpsProfileEnd(double *ms_per_category, uint64_t *launches_per_category) {
   g_profiling = false;
   for (int c = 0; c < kNumCategories; ++c) {

@@ -68,7 +68,9 @@ struct GemmParams {
   int out_vec_ok;   // rows of out / residual can be accessed with 16-byte vectors
   int bias_vec_ok;  // bias is 16-byte aligned
   int num_m_blocks, num_n_blocks;
-  int cta_group;  // 1: one CTA per 128 x 256 tile; 2: CTA pairs on 256 x 256 tiles
+  int cta_group;  // 1: one CTA per 128 x bn tile; 2: CTA pairs on 256 x bn tiles
+  int bn;         // tile width in output columns: 256, 192 or 128 (accumulators stay 256 TMEM columns apart)
+  int cw;         // columns per staged output chunk: 64 (16-bit output, 128-byte rows) or 32
   uint32_t *err;
 #ifdef MDC_GEMM_TRACE
   unsigned long long *trace;  // [grid][8] cycle counters (debug builds only)
@@ -188,10 +190,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int cta_rank = CG == 2 ? static_cast<int>(cluster_ctarank()) : 0;
   const bool leader = cta_rank == 0;
   const int worker = static_cast<int>(blockIdx.x) / CG, num_workers = static_cast<int>(gridDim.x) / CG;
-  // tiles are counted in units of (CG * 128) rows x 256 columns
+  // tiles are (CG * 128) rows x bn columns, numbered with the column block running fastest:
+  // the workers that run side by side then share their rows of A (read from HBM once, found
+  // in L2 by the other column blocks) while W, which is small, stays in L2 throughout
   const int num_m_units = (p.num_m_blocks + CG - 1) / CG;
   const int num_tiles = num_m_units * p.num_n_blocks;
   const int num_kb = (p.K + BK - 1) / BK;
+  const int bn = p.bn;  // tile width; this CTA stages bn / CG rows of W per k-block
+  const uint32_t stage_tx_bytes = static_cast<uint32_t>(A_BYTES + (bn / CG) * BK * 2);
 
   if (threadIdx.x == 0) {
     abort_flag_s = 0;
@@ -230,7 +236,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = worker; ok && tile < num_tiles; tile += num_workers) {
-        const int m_blk = (tile % num_m_units) * CG + cta_rank, n_blk = tile / num_m_units;
+        const int m_blk = (tile / p.num_n_blocks) * CG + cta_rank, n_blk = tile % p.num_n_blocks;
         for (int kb = 0; kb < num_kb; ++kb) {
           { TRACE_T0();
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
@@ -244,13 +250,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if constexpr (CG == 2) {
             // both CTAs' copies complete on the LEADER's barrier, which expects the bytes of both
             const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);
-            if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+            if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * stage_tx_bytes);
             tma_load_2d_cg2(sa, &tmap_a, bar, kb * BK, m_blk * BM);
-            tma_load_2d_cg2(sb, &tmap_b, bar, kb * BK, n_blk * BN + cta_rank * C::B_ROWS);
+            tma_load_2d_cg2(sb, &tmap_b, bar, kb * BK, n_blk * bn + cta_rank * (bn / 2));
           } else {
-            mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+            mbar_arrive_expect_tx(&full_bar[stage], stage_tx_bytes);
             tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m_blk * BM);
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n_blk * BN);
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n_blk * bn);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -259,7 +265,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) ------------------------------
     if (lane == 0 && leader) {
-      constexpr uint32_t idesc = make_idesc_f16(BM * CG, BN, std::is_same<T16, __nv_bfloat16>::value, false, false);
+      const uint32_t idesc = make_idesc_f16(BM * CG, static_cast<uint32_t>(bn),
+                                            std::is_same<T16, __nv_bfloat16>::value, false, false);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -333,7 +340,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t acc_empty_addr0 = mapa_u32(smem_u32(&acc_empty_bar[0]), 0);
     const uint32_t acc_empty_addr1 = mapa_u32(smem_u32(&acc_empty_bar[1]), 0);
     for (int tile = worker; tile < num_tiles; tile += num_workers) {
-      const int m_blk = (tile % num_m_units) * CG + cta_rank, n_blk = tile / num_m_units;
+      const int m_blk = (tile / p.num_n_blocks) * CG + cta_rank, n_blk = tile % p.num_n_blocks;
       { TRACE_T0();
       if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag)) {
         atomicCAS(p.err, 0u, 0x40000000u | static_cast<uint32_t>(acc));
@@ -347,15 +354,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // four 32-column pieces; the load of the next piece is in flight while this one goes
         // through bias / activation / residual.  Output leaves in chunks of CW columns
         // (128 bytes per row): swizzled staging buffer -> one TMA store. ----
-        constexpr int CW = sizeof(TOut) == 2 ? 64 : 32;   // columns per staged chunk
-        constexpr int SUBS = CW / 32;                      // 32-column pieces per chunk
-        constexpr int RES_ROW_BYTES = CW * 2;              // residual is 16-bit
+        // chunk = cw columns; its staged rows are cw * sizeof(TOut) bytes (128, or 64 when a
+        // 16-bit tile half is not a multiple of 64 columns), residual rows cw * 2 bytes
+        const int cw = p.cw;
+        const int SUBS = cw / 32;                          // 32-column pieces per chunk
+        const int OUT_ROW_BYTES = cw * static_cast<int>(sizeof(TOut));
+        const int RES_ROW_BYTES = cw * 2;                  // residual is 16-bit
+        const int half_cols = bn / 2;
         const int row0 = m_blk * BM + quarter * 32;
-        const int gcol_base = n_blk * BN + half_sel * (BN / 2);
-        const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * BN + half_sel * (BN / 2)) +
+        const int gcol_base = n_blk * bn + half_sel * half_cols;
+        const uint32_t t_base = tmem_base + static_cast<uint32_t>(acc * BN + half_sel * half_cols) +
                                 (static_cast<uint32_t>(quarter * 32) << 16);
         // pieces that hold real columns (uniform across the warp; N is a multiple of 4 here)
-        const int n_sub = gcol_base >= p.N ? 0 : min(4, (p.N - gcol_base + 31) / 32);
+        const int n_sub = gcol_base >= p.N ? 0 : min(half_cols / 32, (p.N - gcol_base + 31) / 32);
+        // 16-byte pieces of a staged row are XOR-swizzled the way TMA expects them:
+        // 128-byte rows: piece ^ (row % 8); 64-byte rows: piece ^ ((row / 2) % 4)
+        const int swz_out = OUT_ROW_BYTES == 128 ? (lane & 7) : ((lane >> 1) & 3);
+        const int swz_res = RES_ROW_BYTES == 128 ? (lane & 7) : ((lane >> 1) & 3);
         uint32_t raw[32];
         if (n_sub > 0) tmem_ld_32x32(t_base, raw);
         bool chunk_ok = true;
@@ -401,12 +416,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
               res_phase ^= 1;
             }
-            // this piece is 64 bytes (four 16-byte pieces) of the residual row; the pieces are
-            // XOR-swizzled the way TMA wrote them (128-byte rows: ^ row%8; 64-byte rows: ^ (row/2)%4)
+            // this piece is 64 bytes (four 16-byte pieces) of the residual row
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const int piece = sub_in_chunk * 4 + j;
-              const int phys = RES_ROW_BYTES == 128 ? (piece ^ (lane & 7)) : (piece ^ ((lane >> 1) & 3));
+              const int phys = (sub_in_chunk * 4 + j) ^ swz_res;
               float rv[8];
               load_res8(reinterpret_cast<const T16 *>(my_res + lane * RES_ROW_BYTES + (phys << 4)), rv);
 #pragma unroll
@@ -415,9 +428,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           if constexpr (sizeof(TOut) == 2) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {  // 32 columns = four 16-byte pieces of the 128-byte row
-              const int piece = sub_in_chunk * 4 + j;
-              store_out8<TOut>(reinterpret_cast<TOut *>(my_out + lane * 128 + ((piece ^ (lane & 7)) << 4)), v + 8 * j);
+            for (int j = 0; j < 4; ++j) {  // 32 columns = four 16-byte pieces of the staged row
+              const int phys = (sub_in_chunk * 4 + j) ^ swz_out;
+              store_out8<TOut>(reinterpret_cast<TOut *>(my_out + lane * OUT_ROW_BYTES + (phys << 4)), v + 8 * j);
             }
           } else {
 #pragma unroll
@@ -439,9 +452,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row = m_blk * BM + quarter * 32 + lane;
       const bool row_ok = row < p.M;
 #pragma unroll 1
-      for (int chunk = 0; chunk < BN / 2 / 32; ++chunk) {
-        const int col0 = half_sel * (BN / 2) + chunk * 32;
-        const int gcol0 = n_blk * BN + col0;
+      for (int chunk = 0; chunk < bn / 2 / 32; ++chunk) {
+        const int col0 = half_sel * (bn / 2) + chunk * 32;
+        const int gcol0 = n_blk * bn + col0;
         if (gcol0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + static_cast<uint32_t>(acc * BN + col0) +
@@ -632,6 +645,36 @@ static int choose_cta_group(int64_t M) {
   return M > gemm::BM ? 2 : 1;
 }
 
+// Tile width.  A Gemm takes ceil(tiles / workers) waves of tiles; the last wave is as long as
+// the others however few tiles it holds, so for some shapes a narrower tile (more, cheaper
+// tiles) wastes less: e.g. M = 32768, N = 768 on 74 CTA pairs is 6 waves of 256-wide tiles
+// (5.2 needed) but 7 waves of 192-wide ones (6.9 needed) at 3/4 of the cost each.
+// MDC_GEMM_BN=256|192|128 overrides (for measurements).
+static int choose_bn(int64_t M, int64_t N, int cta_group, int sms) {
+  static const int forced = [] {
+    const char *e = getenv("MDC_GEMM_BN");
+    return e ? atoi(e) : 0;
+  }();
+  if (forced == 256 || forced == 192 || forced == 128) return forced;
+  const int64_t workers = sms / cta_group > 0 ? sms / cta_group : 1;
+  const int64_t m_units = (M + gemm::BM * cta_group - 1) / (gemm::BM * cta_group);
+  int best = 256;
+  double best_cost = 1e300;
+  for (int bn : {256, 192, 128}) {
+    const int64_t tiles = m_units * ((N + bn - 1) / bn);
+    const int64_t waves = (tiles + workers - 1) / workers;
+    // per-tile cost: measured, a 192-wide tile takes about 0.95 of the time of a 256-wide one
+    // (the k-block time is set by operand delivery into shared memory, which shrinks only
+    // from 32 to 28 KiB per CTA), a 128-wide one about 0.8
+    const double cost = static_cast<double>(waves) * (bn == 256 ? 1.0 : bn == 192 ? 0.95 : 0.8);
+    if (cost < best_cost * 0.97) {  // prefer the wider tile unless the gain is clear
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
 // persistent grid: one worker (CTA or CTA pair) per tile up to the number the device holds
 static int gemm_grid(const GemmParams &p, int sms) {
   const int cg = p.cta_group;
@@ -662,15 +705,17 @@ MDC_API void mgpuMatmulEx16(const void *a, const void *w_nk, const float *bias, 
   if (!err) return;
 
   const int cta_group = choose_cta_group(M);
+  const int bn = choose_bn(M, N, cta_group, di.sms);
   CUtensorMap ta, tb;
   if (!encode_tmap_2d(&ta, a, dtype, static_cast<uint64_t>(Kp), static_cast<uint64_t>(M),
                       static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BM) ||
       !encode_tmap_2d(&tb, w_nk, dtype, static_cast<uint64_t>(Kp), static_cast<uint64_t>(N),
-                      static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BN / cta_group))
+                      static_cast<uint64_t>(Kp) * 2, gemm::BK, bn / cta_group))
     return;
 
   GemmParams p;
   p.cta_group = cta_group;
+  p.bn = bn;
   p.M = static_cast<int>(M);
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(Kp);
@@ -686,17 +731,20 @@ MDC_API void mgpuMatmulEx16(const void *a, const void *w_nk, const float *bias, 
   // bias readable as float4
   p.tma_epi = p.out_vec_ok && (!bias || p.bias_vec_ok);
   CUtensorMap to = ta, tr = ta;  // placeholders when the direct-store epilogue is used
+  // staged chunks of 64 columns (128-byte rows) for 16-bit output when a tile half is a
+  // multiple of 64 columns, else 32 columns
+  const uint32_t cw = (out_elem == 2 && (bn / 2) % 64 == 0) ? 64 : 32;
+  p.cw = static_cast<int>(cw);
   if (p.tma_epi) {
-    const uint32_t cw = out_elem == 2 ? 64 : 32;
     if (!encode_tmap_2d_ex(&to, out, out_dtype, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
-                           static_cast<uint64_t>(N) * out_elem, cw, 32, 128))
+                           static_cast<uint64_t>(N) * out_elem, cw, 32, static_cast<int>(cw * out_elem)))
       return;
     if (residual && !encode_tmap_2d_ex(&tr, residual, dtype, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
-                                       static_cast<uint64_t>(N) * 2, cw, 32, cw == 64 ? 128 : 64))
+                                       static_cast<uint64_t>(N) * 2, cw, 32, static_cast<int>(cw * 2)))
       return;
   }
   p.num_m_blocks = static_cast<int>((M + gemm::BM - 1) / gemm::BM);
-  p.num_n_blocks = static_cast<int>((N + gemm::BN - 1) / gemm::BN);
+  p.num_n_blocks = static_cast<int>((N + bn - 1) / bn);
   p.err = err;
 #ifdef MDC_GEMM_TRACE
   p.trace = g_gemm_trace;
@@ -806,14 +854,17 @@ MDC_API void mgpuMatmulNoAlloc(float *input, float *weight, float *bias, float *
   mgpuPackWeight(weight, w16, K, N, MGPU_DTYPE_F16, stream);
 
   const int cta_group = choose_cta_group(M);
+  const int bn = choose_bn(M, N, cta_group, di.sms);
   CUtensorMap ta, tb;
   if (!encode_tmap_2d(&ta, a16, MGPU_DTYPE_F16, static_cast<uint64_t>(Kp), static_cast<uint64_t>(M),
                       static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BM) ||
       !encode_tmap_2d(&tb, w16, MGPU_DTYPE_F16, static_cast<uint64_t>(Kp), static_cast<uint64_t>(N),
-                      static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BN / cta_group))
+                      static_cast<uint64_t>(Kp) * 2, gemm::BK, bn / cta_group))
     return;
   GemmParams p;
   p.cta_group = cta_group;
+  p.bn = bn;
+  p.cw = 32;  // fp32 output: 32 columns per 128-byte staged row
   p.M = static_cast<int>(M);
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(Kp);
@@ -824,7 +875,7 @@ MDC_API void mgpuMatmulNoAlloc(float *input, float *weight, float *bias, float *
   p.bias_vec_ok = bias && !(reinterpret_cast<uintptr_t>(bias) & 15u);
   p.tma_epi = p.out_vec_ok && (!bias || p.bias_vec_ok);
   p.num_m_blocks = static_cast<int>((M + gemm::BM - 1) / gemm::BM);
-  p.num_n_blocks = static_cast<int>((N + gemm::BN - 1) / gemm::BN);
+  p.num_n_blocks = static_cast<int>((N + bn - 1) / bn);
   // the library's own status word if it exists already (so mgpuOpsCheckDeviceStatus sees a
   // kernel that gave up), else the word at the head of the fixed array
   p.err = g_err_slot ? g_err_slot : status;

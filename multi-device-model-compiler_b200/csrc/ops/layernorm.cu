@@ -97,106 +97,131 @@ __device__ __forceinline__ void store_vec<__nv_bfloat16, 8>(__nv_bfloat16 *dst, 
 
 constexpr int kLnWarpsPerBlock = 4;
 
-// One warp per row.  n must be a multiple of EPC, rows 16-byte aligned, and
-// n <= 32 * MAXI * EPC.  Lane l owns chunks l, l+32, ... (coalesced 512-byte warp accesses).
-template <typename TIn, typename TOut, int MAXI>
-__global__ void __launch_bounds__(kLnWarpsPerBlock * 32)
+// One warp per row, persistent: a warp walks rows warp_id, warp_id + total_warps, ... and
+// has the NEXT row's 128-bit loads in flight while it reduces and writes the current one
+// (short 16-bit rows would otherwise leave too few bytes in flight per SM).  n must be a
+// multiple of EPC, rows 16-byte aligned, and n <= 32 * MAXI * EPC.  Lane l owns chunks
+// l, l+32, ... (coalesced 512-byte warp accesses).
+template <typename TIn, typename TOut, int MAXI, bool RES>
+__global__ void __launch_bounds__(kLnWarpsPerBlock * 32, (MAXI > 8 || sizeof(TIn) == 4) ? 2 : (RES ? 4 : 6))
 layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residual,
                       const float *__restrict__ gamma, const float *__restrict__ beta,
                       TIn *__restrict__ sum_out, TOut *__restrict__ y, float eps, int64_t m, int n) {
   constexpr int EPC = LnTraits<TIn>::EPC;
   const int lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t total_warps = static_cast<int64_t>(gridDim.x) * kLnWarpsPerBlock;
+  int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= m) return;
   const int nchunks = n / EPC;
-  const uint4 *xr = reinterpret_cast<const uint4 *>(x + row * n);
-  const uint4 *rr = residual ? reinterpret_cast<const uint4 *>(residual + row * n) : nullptr;
+  constexpr bool has_res = RES;
+  constexpr bool kPrefetch = sizeof(TIn) == 2;
 
-  float v[MAXI][EPC];
-  uint4 raw[MAXI];
+  uint4 raw[MAXI], raw_res[RES ? MAXI : 1];
+  auto fetch = [&](int64_t rw) {
+    const uint4 *xr = reinterpret_cast<const uint4 *>(x + rw * n);
 #pragma unroll
-  for (int i = 0; i < MAXI; ++i) {
-    const int c = lane + 32 * i;
-    if (c < nchunks) raw[i] = __ldcs(xr + c);
-  }
+    for (int i = 0; i < MAXI; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nchunks) raw[i] = __ldcs(xr + c);
+    }
+    if constexpr (has_res) {
+      const uint4 *rr = reinterpret_cast<const uint4 *>(residual + rw * n);
 #pragma unroll
-  for (int i = 0; i < MAXI; ++i) {
-    const int c = lane + 32 * i;
-    if (c < nchunks) LnTraits<TIn>::unpack(raw[i], v[i]);
-  }
-  if (rr) {
+      for (int i = 0; i < MAXI; ++i) {
+        const int c = lane + 32 * i;
+        if (c < nchunks) raw_res[i] = __ldcs(rr + c);
+      }
+    }
+  };
+  fetch(row);
+
+  for (; row < m;) {
+    float v[MAXI][EPC];
+#pragma unroll
+    for (int i = 0; i < MAXI; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nchunks) LnTraits<TIn>::unpack(raw[i], v[i]);
+    }
+    if constexpr (has_res) {
+#pragma unroll
+      for (int i = 0; i < MAXI; ++i) {
+        const int c = lane + 32 * i;
+        if (c < nchunks) {
+          float r[EPC];
+          LnTraits<TIn>::unpack(raw_res[i], r);
+#pragma unroll
+          for (int e = 0; e < EPC; ++e) v[i][e] = LnTraits<TIn>::round(v[i][e] + r[e]);
+          if (sum_out) store_vec<TIn, EPC>(sum_out + row * n + static_cast<int64_t>(c) * EPC, v[i]);
+        }
+      }
+    }
+    // 16-bit rows are short: keep the next row's loads in flight during the reduction and
+    // the stores below.  fp32 rows carry enough bytes per warp; there one row per warp (and
+    // the higher occupancy of the smaller register footprint) is faster.
+    const int64_t next = kPrefetch ? row + total_warps : m;
+    if (next < m) fetch(next);
+
+    // per-lane Welford triple (count, mean, M2) over the lane's own elements
+    float cnt = 0.f, mean = 0.f, m2 = 0.f;
+    {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < MAXI; ++i)
+        if (lane + 32 * i < nchunks) {
+#pragma unroll
+          for (int e = 0; e < EPC; ++e) s += v[i][e];
+          cnt += static_cast<float>(EPC);
+        }
+      mean = cnt > 0.f ? s / cnt : 0.f;
+#pragma unroll
+      for (int i = 0; i < MAXI; ++i)
+        if (lane + 32 * i < nchunks) {
+#pragma unroll
+          for (int e = 0; e < EPC; ++e) {
+            const float d = v[i][e] - mean;
+            m2 = fmaf(d, d, m2);
+          }
+        }
+    }
+    // Chan's merge of two Welford triples, butterfly over the warp
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float cnt_o = __shfl_xor_sync(0xffffffffu, cnt, off);
+      const float mean_o = __shfl_xor_sync(0xffffffffu, mean, off);
+      const float m2_o = __shfl_xor_sync(0xffffffffu, m2, off);
+      const float tot = cnt + cnt_o;
+      if (tot > 0.f) {
+        const float delta = mean_o - mean;
+        const float w = cnt_o / tot;
+        mean = fmaf(delta, w, mean);
+        m2 = m2 + m2_o + delta * delta * cnt * w;
+      }
+      cnt = tot;
+    }
+    // the two sides of a merge round differently in the last bit: take lane 0's result
+    mean = __shfl_sync(0xffffffffu, mean, 0);
+    m2 = __shfl_sync(0xffffffffu, m2, 0);
+    const float rstd = rsqrtf(m2 / static_cast<float>(n) + eps);
+
 #pragma unroll
     for (int i = 0; i < MAXI; ++i) {
       const int c = lane + 32 * i;
       if (c < nchunks) {
-        float r[EPC];
-        LnTraits<TIn>::unpack(__ldcs(rr + c), r);
+        float o[EPC];
 #pragma unroll
-        for (int e = 0; e < EPC; ++e) v[i][e] = LnTraits<TIn>::round(v[i][e] + r[e]);
-        if (sum_out) store_vec<TIn, EPC>(sum_out + row * n + static_cast<int64_t>(c) * EPC, v[i]);
-      }
-    }
-  }
-
-  // per-lane Welford triple (count, mean, M2) over the lane's own elements
-  float cnt = 0.f, mean = 0.f, m2 = 0.f;
-  {
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < MAXI; ++i)
-      if (lane + 32 * i < nchunks) {
-#pragma unroll
-        for (int e = 0; e < EPC; ++e) s += v[i][e];
-        cnt += static_cast<float>(EPC);
-      }
-    mean = cnt > 0.f ? s / cnt : 0.f;
-#pragma unroll
-    for (int i = 0; i < MAXI; ++i)
-      if (lane + 32 * i < nchunks) {
-#pragma unroll
-        for (int e = 0; e < EPC; ++e) {
-          const float d = v[i][e] - mean;
-          m2 = fmaf(d, d, m2);
+        for (int e4 = 0; e4 < EPC / 4; ++e4) {
+          float4 g = make_float4(1.f, 1.f, 1.f, 1.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (gamma) g = __ldg(reinterpret_cast<const float4 *>(gamma) + c * (EPC / 4) + e4);
+          if (beta) b = __ldg(reinterpret_cast<const float4 *>(beta) + c * (EPC / 4) + e4);
+          o[4 * e4 + 0] = fmaf((v[i][4 * e4 + 0] - mean) * rstd, g.x, b.x);
+          o[4 * e4 + 1] = fmaf((v[i][4 * e4 + 1] - mean) * rstd, g.y, b.y);
+          o[4 * e4 + 2] = fmaf((v[i][4 * e4 + 2] - mean) * rstd, g.z, b.z);
+          o[4 * e4 + 3] = fmaf((v[i][4 * e4 + 3] - mean) * rstd, g.w, b.w);
         }
+        store_vec<TOut, EPC>(y + row * n + static_cast<int64_t>(c) * EPC, o);
       }
-  }
-  // Chan's merge of two Welford triples, butterfly over the warp
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    const float cnt_o = __shfl_xor_sync(0xffffffffu, cnt, off);
-    const float mean_o = __shfl_xor_sync(0xffffffffu, mean, off);
-    const float m2_o = __shfl_xor_sync(0xffffffffu, m2, off);
-    const float tot = cnt + cnt_o;
-    if (tot > 0.f) {
-      const float delta = mean_o - mean;
-      const float w = cnt_o / tot;
-      mean = fmaf(delta, w, mean);
-      m2 = m2 + m2_o + delta * delta * cnt * w;
     }
-    cnt = tot;
-  }
-  // the two sides of a merge round differently in the last bit: take lane 0's result
-  mean = __shfl_sync(0xffffffffu, mean, 0);
-  m2 = __shfl_sync(0xffffffffu, m2, 0);
-  const float rstd = rsqrtf(m2 / static_cast<float>(n) + eps);
-
-#pragma unroll
-  for (int i = 0; i < MAXI; ++i) {
-    const int c = lane + 32 * i;
-    if (c < nchunks) {
-      float o[EPC];
-#pragma unroll
-      for (int e4 = 0; e4 < EPC / 4; ++e4) {
-        float4 g = make_float4(1.f, 1.f, 1.f, 1.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (gamma) g = __ldg(reinterpret_cast<const float4 *>(gamma) + c * (EPC / 4) + e4);
-        if (beta) b = __ldg(reinterpret_cast<const float4 *>(beta) + c * (EPC / 4) + e4);
-        o[4 * e4 + 0] = fmaf((v[i][4 * e4 + 0] - mean) * rstd, g.x, b.x);
-        o[4 * e4 + 1] = fmaf((v[i][4 * e4 + 1] - mean) * rstd, g.y, b.y);
-        o[4 * e4 + 2] = fmaf((v[i][4 * e4 + 2] - mean) * rstd, g.z, b.z);
-        o[4 * e4 + 3] = fmaf((v[i][4 * e4 + 3] - mean) * rstd, g.w, b.w);
-      }
-      store_vec<TOut, EPC>(y + row * n + static_cast<int64_t>(c) * EPC, o);
-    }
+    row = next;
   }
 }
 
@@ -269,19 +294,26 @@ static void launch_layernorm(const void *x, const void *residual, const float *g
   TOut *yo = static_cast<TOut *>(y);
   if (vec_ok) {
     const int per_lane = static_cast<int>((n / EPC + 31) / 32);
-    const unsigned grid = static_cast<unsigned>((m + kLnWarpsPerBlock - 1) / kLnWarpsPerBlock);
+    // persistent: at most 16 blocks of 4 warps per SM, each warp walking several rows
+    const int64_t blocks_needed = (m + kLnWarpsPerBlock - 1) / kLnWarpsPerBlock;
+    const int64_t blocks_cap = static_cast<int64_t>(device_info().sms) * 16;
+    const unsigned grid = static_cast<unsigned>(
+        (sizeof(TIn) == 2 && blocks_needed > blocks_cap) ? blocks_cap : blocks_needed);
     const int threads = kLnWarpsPerBlock * 32;
     const int ni = static_cast<int>(n);
-    if (per_lane <= 2)
-      layernorm_warp_kernel<TIn, TOut, 2><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni);
-    else if (per_lane <= 4)
-      layernorm_warp_kernel<TIn, TOut, 4><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni);
-    else if (per_lane <= 6)
-      layernorm_warp_kernel<TIn, TOut, 6><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni);
-    else if (per_lane <= 8)
-      layernorm_warp_kernel<TIn, TOut, 8><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni);
-    else
-      layernorm_warp_kernel<TIn, TOut, 16><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni);
+#define MDC_LN_LAUNCH(MAXI_)                                                                          \
+  do {                                                                                            \
+    if (ri)                                                                                       \
+      layernorm_warp_kernel<TIn, TOut, MAXI_, true><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni);  \
+    else                                                                                          \
+      layernorm_warp_kernel<TIn, TOut, MAXI_, false><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni); \
+  } while (0)
+    if (per_lane <= 2) MDC_LN_LAUNCH(2);
+    else if (per_lane <= 4) MDC_LN_LAUNCH(4);
+    else if (per_lane <= 6) MDC_LN_LAUNCH(6);
+    else if (per_lane <= 8) MDC_LN_LAUNCH(8);
+    else MDC_LN_LAUNCH(16);
+#undef MDC_LN_LAUNCH
     launched("layernorm_warp_kernel");
   } else {
     const size_t smem = static_cast<size_t>(n) * sizeof(float);

@@ -115,3 +115,31 @@ def test_linearity_at_full_size(m):
     # equal up to the order of the fp32 accumulation
     assert oracle.max_rel_err(y12, y) <= 5e-3
     assert np.max(np.abs(y12 - y)) <= 1e-4
+
+
+@pytest.mark.parametrize("M,N,K", [(32768, 768, 64), (1024, 128, 64), (8192, 768, 192)])
+def test_narrow_tiles_are_exact(m, M, N, K):
+    # shapes for which the library picks 192- or 128-column tiles (fewer wasted tiles in the
+    # last wave); small integers again, so the result must match exactly, with every epilogue
+    # input in play (bias and residual are integers too)
+    rng = np.random.default_rng(7)
+    a = rng.integers(-3, 4, (M, K)).astype(np.float32)
+    w = rng.integers(-2, 3, (K, N)).astype(np.float32)
+    b = rng.integers(-4, 5, N).astype(np.float32)
+    r = rng.integers(-8, 9, (M, N)).astype(np.float32)
+    ref = a @ w + b + r
+    assert np.array_equal(m.matmul16(a, w, bias=b, residual=r), ref)              # 16-bit output
+    assert np.array_equal(m.matmul16(a, w, bias=b, residual=r, out_dtype=m.F32), ref)
+
+
+@pytest.mark.parametrize("bn", ["192", "128"])
+def test_forced_tile_width(bn):
+    # every shape of this file again with the tile width forced (read once per process)
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, MDC_GEMM_BN=bn)
+    r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-m", "gpu", "-x",
+                        "-k", "small_integers or ragged or epilogues or narrow"],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
