@@ -238,7 +238,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--chunks", type=int, default=4, help="pipeline depth of the host-buffer (e2e) path")
+    ap.add_argument("--chunks", type=int, default=3, help="pipeline depth of the host-buffer (e2e) path")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only-timed", action="store_true",
                     help="stop after the device-resident timed region (used for the ncu launch list)")

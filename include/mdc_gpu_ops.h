@@ -146,7 +146,9 @@ void mgpuEncoderStackDestroy(void *stack);
 
 /* Host-buffer form of Run: x and y are HOST pointers (pinned for full speed).  The batch
  * is cut into `chunks` pieces whose upload, compute and download overlap on three
- * streams; returns after y is complete.  seq_lens is a host pointer (or NULL). */
+ * streams (with 3 or more chunks the first and last are batch/8 sequences, because only
+ * their copies are exposed); returns after y is complete.  seq_lens is a host pointer (or
+ * NULL). */
 void mgpuEncoderStackRunHost(void *stack, const float *x_host, const int32_t *seq_lens_host,
                              float *y_host, int64_t batch, int64_t seq_len, int32_t chunks);
 

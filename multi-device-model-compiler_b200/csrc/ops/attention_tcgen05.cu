@@ -128,6 +128,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  pdl_wait();  // set-up above overlaps the previous kernel's tail; QKV is read below
 
   if (warp == 4) {
     // ------------------------------ loads + MMA issue ------------------------------
@@ -412,7 +413,7 @@ MDC_API void mgpuAttention(const void *qkv, const int32_t *seq_lens, void *out, 
         return;
       set = true;
     }
-    kern<<<grid, attn::THREADS, attn::SMEM_BYTES, s>>>(tm, p);
+    check_cuda(launch_chain(kern, grid, dim3(attn::THREADS), attn::SMEM_BYTES, s, 1, tm, p), "launch attention");
   } else {
     auto kern = attention_tcgen05_kernel<__nv_bfloat16>;
     static bool set = false;
@@ -422,7 +423,7 @@ MDC_API void mgpuAttention(const void *qkv, const int32_t *seq_lens, void *out, 
         return;
       set = true;
     }
-    kern<<<grid, attn::THREADS, attn::SMEM_BYTES, s>>>(tm, p);
+    check_cuda(launch_chain(kern, grid, dim3(attn::THREADS), attn::SMEM_BYTES, s, 1, tm, p), "launch attention");
   }
   launched("attention_tcgen05_kernel");
 }

@@ -9,6 +9,14 @@ namespace mdc {
 
 std::atomic<uint64_t> g_launch_count{0};
 
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char *e = getenv("MDC_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 bool g_profiling = false;
 namespace {
 struct ProfileSpan {
@@ -94,6 +102,7 @@ __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <typename T16>
 __global__ void __launch_bounds__(kEwBlock)
 cast_f32_to_16(const float *__restrict__ src, T16 *__restrict__ dst, int64_t n) {
+  pdl_wait();
   const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
   if (aligned16(src) && aligned16(dst)) {
@@ -292,9 +301,9 @@ MDC_API void mgpuCast(const void *src, int32_t sd, void *dst, int32_t dd, int64_
     return;
   }
   if (sd == MGPU_DTYPE_F32 && dd == MGPU_DTYPE_F16)
-    cast_f32_to_16<__half><<<grid, kEwBlock, 0, s>>>((const float *)src, (__half *)dst, n);
+    check_cuda(launch_chain(cast_f32_to_16<__half>, dim3(grid), dim3(kEwBlock), 0, s, 1, (const float *)src, (__half *)dst, n), "launch cast");
   else if (sd == MGPU_DTYPE_F32 && dd == MGPU_DTYPE_BF16)
-    cast_f32_to_16<__nv_bfloat16><<<grid, kEwBlock, 0, s>>>((const float *)src, (__nv_bfloat16 *)dst, n);
+    check_cuda(launch_chain(cast_f32_to_16<__nv_bfloat16>, dim3(grid), dim3(kEwBlock), 0, s, 1, (const float *)src, (__nv_bfloat16 *)dst, n), "launch cast");
   else if (sd == MGPU_DTYPE_F16 && dd == MGPU_DTYPE_F32)
     cast_16_to_f32<__half><<<grid, kEwBlock, 0, s>>>((const __half *)src, (float *)dst, n);
   else if (sd == MGPU_DTYPE_BF16 && dd == MGPU_DTYPE_F32)

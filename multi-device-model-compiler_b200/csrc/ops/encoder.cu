@@ -252,9 +252,24 @@ MDC_API void mgpuEncoderStackRunHost(void *stack, const float *x_host, const int
   EncoderStack *st = static_cast<EncoderStack *>(stack);
   if (!st) { fail("mgpuEncoderStackRunHost: null handle"); return; }
   if (batch <= 0 || seq_len <= 0) return;
+  // Chunk sizes.  Only the first chunk's upload and the last chunk's download are exposed
+  // (everything else overlaps compute), while small chunks run the kernels less efficiently:
+  // so the first and the last chunk are small (batch / 8) and the rest is split evenly.
   if (chunks < 1) chunks = 1;
   if (chunks > batch) chunks = static_cast<int32_t>(batch);
-  const int64_t per = (batch + chunks - 1) / chunks;
+  std::vector<int64_t> sizes;
+  if (chunks <= 2 || batch < 16) {
+    const int64_t even = (batch + chunks - 1) / chunks;
+    for (int64_t b0 = 0; b0 < batch; b0 += even) sizes.push_back(batch - b0 < even ? batch - b0 : even);
+  } else {
+    const int64_t edge = batch / 8 > 0 ? batch / 8 : 1;
+    const int64_t mid = batch - 2 * edge, parts = chunks - 2;
+    sizes.push_back(edge);
+    for (int64_t i = 0; i < parts; ++i) sizes.push_back(mid / parts + (i < mid % parts ? 1 : 0));
+    sizes.push_back(edge);
+  }
+  int64_t per = 0;  // largest chunk: sizes the device buffers and the workspace
+  for (int64_t v : sizes) per = v > per ? v : per;
   const int64_t d = st->d;
   if (!st->s_in) {
     bool ok = check_cuda(cudaStreamCreateWithFlags(&st->s_in, cudaStreamNonBlocking), "stream") &&
@@ -284,9 +299,11 @@ MDC_API void mgpuEncoderStackRunHost(void *stack, const float *x_host, const int
   order_after_previous(st, st->s_comp);
   if (!ensure_ws(st, per * seq_len, st->s_comp)) return;
   int n = 0;
-  for (int64_t b0 = 0; b0 < batch; b0 += per, ++n) {
+  int64_t b0 = 0;
+  for (size_t ci = 0; ci < sizes.size(); b0 += sizes[ci], ++ci, ++n) {
     const int set = n & 1;
-    const int64_t nb = (batch - b0 < per) ? batch - b0 : per;
+    const int64_t nb = sizes[ci];
+    if (nb <= 0) continue;
     const size_t elems = static_cast<size_t>(nb) * seq_len * d;
     const size_t off = static_cast<size_t>(b0) * seq_len * d;
     if (n >= 2) cudaStreamWaitEvent(st->s_in, st->ev_comp[set], 0);  // x_dev[set] consumed

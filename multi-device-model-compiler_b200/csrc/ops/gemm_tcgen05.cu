@@ -228,6 +228,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if constexpr (CG == 2) cluster_sync_all();  // the peer's barriers exist before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  pdl_wait();  // everything above overlaps the previous kernel's tail; operands are read below
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -593,23 +594,8 @@ static void launch_gemm_cg(const CUtensorMap &ta, const CUtensorMap &tb, const C
   }
   {
     ProfileScope prof(kCatGemm, s);
-    if constexpr (CG == 2) {
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(static_cast<unsigned>(grid));
-      cfg.blockDim = dim3(gemm::THREADS);
-      cfg.dynamicSmemBytes = smem;
-      cfg.stream = s;
-      cudaLaunchAttribute attr;
-      attr.id = cudaLaunchAttributeClusterDimension;
-      attr.val.clusterDim.x = 2;
-      attr.val.clusterDim.y = 1;
-      attr.val.clusterDim.z = 1;
-      cfg.attrs = &attr;
-      cfg.numAttrs = 1;
-      check_cuda(cudaLaunchKernelEx(&cfg, kern, ta, tb, to, tr, p), "cudaLaunchKernelEx(gemm pair)");
-    } else {
-      kern<<<grid, gemm::THREADS, smem, s>>>(ta, tb, to, tr, p);
-    }
+    check_cuda(launch_chain(kern, dim3(static_cast<unsigned>(grid)), dim3(gemm::THREADS), smem, s, CG, ta, tb, to, tr, p),
+               "launch gemm");
   }
   launched("gemm_tcgen05_kernel");
 }

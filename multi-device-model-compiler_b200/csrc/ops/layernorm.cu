@@ -108,6 +108,7 @@ layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residua
                       const float *__restrict__ gamma, const float *__restrict__ beta,
                       TIn *__restrict__ sum_out, TOut *__restrict__ y, float eps, int64_t m, int n) {
   constexpr int EPC = LnTraits<TIn>::EPC;
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t total_warps = static_cast<int64_t>(gridDim.x) * kLnWarpsPerBlock;
   int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarpsPerBlock + (threadIdx.x >> 5);
@@ -304,9 +305,9 @@ static void launch_layernorm(const void *x, const void *residual, const float *g
 #define MDC_LN_LAUNCH(MAXI_)                                                                          \
   do {                                                                                            \
     if (ri)                                                                                       \
-      layernorm_warp_kernel<TIn, TOut, MAXI_, true><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni);  \
+      check_cuda(launch_chain(layernorm_warp_kernel<TIn, TOut, MAXI_, true>, dim3(grid), dim3(threads), 0, s, 1, xi, ri, gamma, beta, so, yo, eps, m, ni), "launch layernorm");  \
     else                                                                                          \
-      layernorm_warp_kernel<TIn, TOut, MAXI_, false><<<grid, threads, 0, s>>>(xi, ri, gamma, beta, so, yo, eps, m, ni); \
+      check_cuda(launch_chain(layernorm_warp_kernel<TIn, TOut, MAXI_, false>, dim3(grid), dim3(threads), 0, s, 1, xi, ri, gamma, beta, so, yo, eps, m, ni), "launch layernorm"); \
   } while (0)
     if (per_lane <= 2) MDC_LN_LAUNCH(2);
     else if (per_lane <= 4) MDC_LN_LAUNCH(4);

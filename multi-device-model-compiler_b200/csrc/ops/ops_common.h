@@ -5,6 +5,7 @@
 #include <atomic>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -51,6 +52,44 @@ inline size_t dtype_size(int32_t dtype) { return dtype == MGPU_DTYPE_F32 ? 4 : 2
 inline bool dtype_is16(int32_t dtype) { return dtype == MGPU_DTYPE_F16 || dtype == MGPU_DTYPE_BF16; }
 
 inline cudaStream_t as_stream(void *s) { return static_cast<cudaStream_t>(s); }
+
+// Launch helper for the kernels of the layer chain.  With programmatic dependent launch the
+// front end may set the next kernel up (and start its CTAs on SMs the previous kernel has
+// already left) while the previous kernel drains; each such kernel calls pdl_wait() (device,
+// ptx_sm100.cuh / below) before it touches global memory, which orders it after the whole
+// previous grid.  MDC_PDL=0 turns the attribute off (plain stream order).
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                int cluster_x, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attrs[2];
+  unsigned n = 0;
+  if (pdl_enabled()) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_x > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = static_cast<unsigned>(cluster_x);
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#ifdef __CUDACC__
+// Blocks until the grid this one was made dependent on has completed and its writes are
+// visible; returns at once for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
 
 // Optional per-launch timing: while profiling is on (mgpuOpsProfileBegin), every launch
 // site brackets its kernel with two CUDA events on the launching stream; mgpuOpsProfileEnd
