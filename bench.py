@@ -127,6 +127,23 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def max_over_ranks(value, dist, device):
+    """The slowest rank's time: an all-reduce(MAX) over the process group (NCCL on GPUs;
+    the CPU tests run the same code over gloo)."""
+    if dist is None:
+        return float(value)
+    import torch
+    t = torch.tensor([float(value)], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def shard_of(rank, world, batch_per_gpu):
+    """Weak scaling: every rank owns batch_per_gpu sequences; returns (first, count) of its
+    slice of the global batch."""
+    return rank * batch_per_gpu, batch_per_gpu
+
+
 def run_reference(args, rank, world):
     """The reference arm: the CPU restatement of the reference's path (oracle/), all host
     threads, on a bounded sample of the same workload per step."""
@@ -274,13 +291,8 @@ def main():
             import torch
             torch.cuda.synchronize()
 
-    def max_over_ranks(v):
-        if dist is None:
-            return v
-        import torch
-        t = torch.tensor([v], dtype=torch.float64, device=f"cuda:{local_rank}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    def _max(v):
+        return max_over_ranks(v, dist, f"cuda:{local_rank}")
 
     sampler = ClockSampler(local_rank)
     sampler.start()  # nvidia-smi needs a moment before its first sample; runs until the timed region ends
@@ -308,7 +320,7 @@ def main():
     rt.mgpuEventSynchronize(ev1)
     barrier()
     launches = ops.mgpuOpsLaunchCount() - launches0
-    ms_total = max_over_ranks(rt.mgpuEventElapsedTime(ev0, ev1))
+    ms_total = _max(rt.mgpuEventElapsedTime(ev0, ev1))
     clocks = sampler.stop()
     status = ops.mgpuOpsCheckDeviceStatus(stream)
     mdc.check("timed region")
@@ -355,7 +367,7 @@ def main():
         stack.run_host(x, y_host, None, chunks=args.chunks)  # returns when y_host is complete
     rt.mgpuEventRecord(ev1, stream)
     rt.mgpuEventSynchronize(ev1)
-    e2e_ms = max_over_ranks(max(rt.mgpuEventElapsedTime(ev0, ev1), 1e3 * (time.perf_counter() - t0)))
+    e2e_ms = _max(max(rt.mgpuEventElapsedTime(ev0, ev1), 1e3 * (time.perf_counter() - t0)))
     barrier()
     rt.mgpuMemHostUnregister(x.ctypes.data)
     rt.mgpuMemHostUnregister(y_host.ctypes.data)

@@ -184,3 +184,24 @@ def test_gpu_encoder_graph_with_baked_weights(tmp_path):
     for b in range(B):
         n = int(lens[b])
         assert oracle.max_rel_err(ref[b, :n], got[b, :n], floor_frac=1.0) <= 2e-2
+
+
+@pytest.mark.gpu
+def test_gpu_batch_sharding_over_two_devices(tmp_path):
+    # one worker process per GPU, each computing its rows of the batch; the gathered file
+    # must equal the single-GPU result bit for bit (sequences do not interact)
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    lib_path = os.path.join(PKG, "lib", "graph_encoder.so")
+    B, S, d = 8, 128, 768
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((B, S, d)).astype(np.float32)
+    lens = np.full(B, S, np.float32)
+    common = [lib_path, "--input", f"{B}_{S}_{d},{B}", "--output", f"{B}_{S}_{d}", "--data", files(tmp_path, [x, lens])]
+    one, two = str(tmp_path / "one.dat"), str(tmp_path / "two.dat")
+    r1 = run(common + ["--out-data", one])
+    assert r1.returncode == 0, r1.stderr + r1.stdout
+    r2 = run(common + ["--out-data", two, "--gpus", "2", "--rerun", "2", "--json"])
+    assert r2.returncode == 0, r2.stderr + r2.stdout
+    assert np.array_equal(np.fromfile(one, np.float32), np.fromfile(two, np.float32))
