@@ -144,21 +144,68 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
-template <int ACT>
-__device__ __forceinline__ float act_fast(float v) {
+// Two fp32 lanes per instruction (fma.rn.f32x2 and friends, sm_100): the epilogue's
+// arithmetic is issue-bound next to the tensor pipe, and this halves its FMA / MUL count.
+struct F2 {
+  uint64_t v;
+};
+__device__ __forceinline__ F2 f2(float a, float b) {
+  F2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_get(F2 x, float &a, float &b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(x.v));
+}
+__device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) {
+  F2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d.v) : "l"(a.v), "l"(b.v), "l"(c.v));
+  return d;
+}
+__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) {
+  F2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d.v) : "l"(a.v), "l"(b.v));
+  return d;
+}
+__device__ __forceinline__ F2 f2_add(F2 a, F2 b) {
+  F2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d.v) : "l"(a.v), "l"(b.v));
+  return d;
+}
+
+// Exact-erf GELU on two values at once: 0.5 v (1 + sign(v) erf(|v| / sqrt 2)) with
+// y = |v| / sqrt(2) * sqrt(log2 e), so that exp(-x^2) = 2^(-y^2), and p rescaled to match.
+__device__ __forceinline__ void gelu_erf_pair(float &va, float &vb) {
+  const F2 A = f2(fabsf(va), fabsf(vb));
+  const F2 Y = f2_mul(A, f2(0.84932180028f, 0.84932180028f));
+  const F2 NY = f2_mul(A, f2(-0.84932180028f, -0.84932180028f));
+  float da, db;
+  f2_get(f2_fma(f2(0.27273750f, 0.27273750f), Y, f2(1.0f, 1.0f)), da, db);
+  const F2 T = f2(rcp_approx(da), rcp_approx(db));
+  // -(a5 t^4 + ... + a1): the sign is folded into the coefficients
+  F2 P = f2_fma(f2(-1.061405429f, -1.061405429f), T, f2(1.453152027f, 1.453152027f));
+  P = f2_fma(P, T, f2(-1.421413741f, -1.421413741f));
+  P = f2_fma(P, T, f2(0.284496736f, 0.284496736f));
+  P = f2_fma(P, T, f2(-0.254829592f, -0.254829592f));
+  const F2 NQ = f2_mul(P, T);
+  float sa, sb;
+  f2_get(f2_mul(Y, NY), sa, sb);  // -y^2
+  const F2 E = f2(ex2_approx(sa), ex2_approx(sb));
+  const F2 ERF = f2_fma(NQ, E, f2(1.0f, 1.0f));
+  const F2 HALF = f2(0.5f, 0.5f);
+  const F2 G = f2_fma(f2_mul(A, HALF), ERF, f2_mul(f2(va, vb), HALF));
+  f2_get(G, va, vb);
+}
+
+// Applies the activation to n (even) values in place.
+template <int ACT, int N>
+__device__ __forceinline__ void act_fast_n(float *v) {
   if constexpr (ACT == kActGeluErf) {
-    // y = |v| / sqrt(2) * sqrt(log2 e), so that exp(-x^2) = 2^(-y^2); p rescaled to match
-    const float y = fabsf(v) * 0.84932180028f;
-    const float t = rcp_approx(fmaf(0.27273750f, y, 1.0f));
-    float poly = fmaf(1.061405429f, t, -1.453152027f);
-    poly = fmaf(poly, t, 1.421413741f);
-    poly = fmaf(poly, t, -0.284496736f);
-    poly = fmaf(poly, t, 0.254829592f);
-    const float erf_abs = fmaf(-poly * t, ex2_approx(-y * y), 1.0f);
-    const float h = 0.5f * v;
-    return fmaf(fabsf(h), erf_abs, h);  // 0.5 v (1 + sign(v) erf(|v| / sqrt 2))
-  } else {
-    return act_apply_t<ACT>(v);
+#pragma unroll
+    for (int j = 0; j < N; j += 2) gelu_erf_pair(v[j], v[j + 1]);
+  } else if constexpr (ACT != kActNone) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) v[j] = act_apply_t<ACT>(v[j]);
   }
 }
 
@@ -406,8 +453,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             }
           }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = act_fast<ACT>(v[j]);
+          act_fast_n<ACT, 32>(v);
           if (res) {
             if (sub_in_chunk == 0) {
               if (!mbar_wait(&res_bar[ew], res_phase, abort_flag)) {
