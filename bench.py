@@ -205,6 +205,34 @@ def run_micro(args):
         act = mdc.ACT_GELU_ERF if kind == "gemm_gelu" else mdc.ACT_NONE
         fn = lambda: ops.mgpuMatmulEx16(a.ptr, w.ptr, bias.ptr, None, out.ptr, M, N, K, mdc.F16, mdc.F16, act, stream)
         work, unit = 2.0 * M * N * K, "TFLOP/s"
+    elif name == "matmul_c1_abi":
+        # the reference entry point with fp32 operands: cast + weight pack + Gemm per call
+        M, N, K = 2048, 4096, 4096
+        a = mdc.to_device(rng.standard_normal((M, K)).astype(np.float32), stream)
+        w = mdc.to_device((0.02 * rng.standard_normal((K, N))).astype(np.float32), stream)
+        bias = mdc.to_device((0.02 * rng.standard_normal(N)).astype(np.float32), stream)
+        out = mdc.DeviceBuffer(M * N * 4, stream)
+        fn = lambda: ops.mgpuMatmul(a.ptr, w.ptr, bias.ptr, out.ptr, M, N, K, stream)
+        work, unit = 2.0 * M * N * K, "TFLOP/s"
+    elif name == "layer_c3":
+        # one post-LN layer, batch 32, seq 384, valid lengths uniform in [192, 384]
+        Bc, Sc = 32, 384
+        lw = make_weights()[:1]
+        stack = mdc.EncoderStack(lw, H)
+        x = mdc.to_device(rng.standard_normal((Bc, Sc, D)).astype(np.float32), stream)
+        lens = mdc.to_device(rng.integers(192, 385, Bc).astype(np.int32), stream)
+        y = mdc.DeviceBuffer(Bc * Sc * D * 4, stream)
+        fn = lambda: ops.mgpuEncoderStackRun(stack.h, x.ptr, lens.ptr, y.ptr, Bc, Sc, stream)
+        T3 = Bc * Sc
+        work = 2.0 * T3 * (D * 3 * D + D * D + 2 * D * F) + 4.0 * Bc * H * Sc * Sc * 64  # dense count
+        unit = "TFLOP/s"
+    elif name == "attention_c3":
+        Bc, Sc = 32, 384
+        q = mdc.to_device(rng.standard_normal((Bc * Sc, 3 * H * 64)).astype(np.float16), stream)
+        lens = mdc.to_device(rng.integers(192, 385, Bc).astype(np.int32), stream)
+        out = mdc.DeviceBuffer(Bc * Sc * H * 64 * 2, stream)
+        fn = lambda: ops.mgpuAttention(q.ptr, lens.ptr if args.hidden != 1 else None, out.ptr, Bc, Sc, H, 64, False, mdc.F16, stream)
+        work, unit = 4.0 * Bc * H * Sc * Sc * 64, "TFLOP/s"
     elif name == "attention":
         Bq = max(tokens // S, 1)
         q = mdc.to_device(rng.standard_normal((Bq * S, 3 * H * 64)).astype(np.float16), stream)
@@ -248,7 +276,7 @@ def run_micro(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--micro", default=None, help="run one kernel only (for profiling): " + ", ".join(
-        list(MICRO) + ["attention", "layernorm_f32", "layernorm_f16", "add_f32"]))
+        list(MICRO) + ["matmul_c1_abi", "layer_c3", "attention", "attention_c3", "layernorm_f32", "layernorm_f16", "add_f32"]))
     ap.add_argument("--tokens", type=int, default=8192, help="--micro: rows / tokens of the small case")
     ap.add_argument("--hidden", type=int, default=768, help="--micro layernorm_f32 / add_f32: row length")
     ap.add_argument("--gpus", type=int, default=1)

@@ -10,16 +10,18 @@
 //   warp 4, one thread   TMA loads of the Q / K / V tiles (128 x 64, 128-byte swizzle) and
 //                        the two tcgen05.mma groups per key tile:
 //                          S = Q.K^T   (M=128, N=128, K=64)  -> TMEM columns [0,128)
-//                          O_t = P.V   (M=128, N=64, K=128)  -> TMEM columns [128,192)
+//                          O_t = P.V   (M=128, N=64, K=128)  -> TMEM columns [64,128)
+//                        P (16-bit, two keys per 32-bit column) is written by the softmax
+//                        threads over S columns [0,64) they have already consumed and is
+//                        the A operand of the second MMA straight from tensor memory.
 //                        V is used as it lies in memory (keys x head_dim, an MN-major B
 //                        operand), so no transpose pass is needed.
 //   warps 0-3            one thread per query row: tcgen05.ld the scores, running max and
-//                        sum in fp32 (exp2 with log2(e)/sqrt(d) folded in), P written to
-//                        shared memory as the 16-bit A operand of the second MMA, then the
-//                        partial product O_t is read back and accumulated in registers
-//                        with the usual rescaling.
-// Shared memory is 80 KiB and TMEM 256 columns per CTA, so two CTAs share an SM and
-// overlap each other's load / MMA / softmax phases.  Every wait is bounded.
+//                        sum in fp32 (exp2 with log2(e)/sqrt(d) folded in), P stored back
+//                        into tensor memory (tcgen05.st), then the partial product O_t is
+//                        read back and accumulated in registers with the usual rescaling.
+// Shared memory is 49 KiB (Q, K, V tiles only) and TMEM 128 columns per CTA, so three CTAs
+// share an SM and overlap each other's load / MMA / softmax phases.  Every wait is bounded.
 #include <type_traits>
 
 #include "ops_common.h"
@@ -30,11 +32,11 @@ namespace mdc {
 namespace attn {
 constexpr int BQ = 128, BKV = 128, D = 64;
 constexpr int TILE_BYTES = 128 * D * 2;  // 16 KiB: one 128 x 64 16-bit tile
-constexpr int P_BYTES = 2 * TILE_BYTES;  // 128 x 128 P as two 128 x 64 k-blocks
 constexpr int THREADS = 160;
-constexpr int TMEM_COLS = 256;
-constexpr int S_COL = 0, O_COL = 128;
-constexpr size_t SMEM_BYTES = 3 * TILE_BYTES + P_BYTES + 1024;
+constexpr int TMEM_COLS = 128;
+constexpr int S_COL = 0, P_COL = 0, O_COL = 64;
+constexpr int CTAS_PER_SM = 3;
+constexpr size_t SMEM_BYTES = 3 * TILE_BYTES + 1024;
 }  // namespace attn
 
 struct AttnParams {
@@ -90,19 +92,19 @@ __device__ __forceinline__ float ex2_fast(float x) {
 // while step t is still in its softmax: K (and the next item's Q) as soon as S = Q.K^T of
 // step t has been computed, V as soon as P.V of step t has.
 template <typename T16>
-__global__ void __launch_bounds__(attn::THREADS, 2)
+__global__ void __launch_bounds__(attn::THREADS, attn::CTAS_PER_SM)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttnParams p) {
   using namespace attn;
   using namespace ptx;
   extern __shared__ uint8_t smem_dyn[];
-  __shared__ uint64_t bar_q, bar_k, bar_v, bar_s_full, bar_p_ready, bar_o_full;
+  __shared__ uint64_t bar_q, bar_k, bar_v, bar_s_full, bar_p_ready, bar_o_full, bar_o_read;
   __shared__ uint32_t tmem_slot;
   __shared__ uint32_t abort_flag_s;
   volatile uint32_t *abort_flag = &abort_flag_s;
 
   uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
-  uint8_t *sQ = tiles, *sK = tiles + TILE_BYTES, *sV = tiles + 2 * TILE_BYTES, *sP = tiles + 3 * TILE_BYTES;
+  uint8_t *sQ = tiles, *sK = tiles + TILE_BYTES, *sV = tiles + 2 * TILE_BYTES;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_tiles = (p.seq + BQ - 1) / BQ;
@@ -118,6 +120,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
     mbar_init(&bar_s_full, 1);
     mbar_init(&bar_p_ready, 128);
     mbar_init(&bar_o_full, 1);
+    mbar_init(&bar_o_read, 128);
     mbar_init_fence();
   }
   if (warp == 4) {
@@ -136,8 +139,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
       constexpr bool kBf16 = std::is_same<T16, __nv_bfloat16>::value;
       constexpr uint32_t idesc_s = make_idesc_f16(BQ, BKV, kBf16, false, false);
       constexpr uint32_t idesc_o = make_idesc_f16(BQ, D, kBf16, false, true);  // V is MN-major
-      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV),
-                     p_addr = smem_u32(sP);
+      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
       auto load_q = [&](const AttnItem &it) {
         mbar_arrive_expect_tx(&bar_q, TILE_BYTES);
         tma_load_2d(sQ, &tmap_qkv, &bar_q, it.head * D, it.row_base + it.q0);
@@ -176,6 +178,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
           if (!mbar_wait(&bar_q, q_cnt & 1, abort_flag)) { code = 0x51000000u; break; }
           ++q_cnt;
         }
+        // S overwrites the columns that held P and O of the previous step: the softmax
+        // threads must have read that O (the P.V that read P has completed by then)
+        if (t > 0 && !mbar_wait(&bar_o_read, ph ^ 1, abort_flag)) { code = 0x57000000u | (t & 0xffff); break; }
         if (!mbar_wait(&bar_k, ph, abort_flag)) { code = 0x53000000u | (t & 0xffff); break; }
         tc_fence_after();
         {
@@ -198,17 +203,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
         {
 #pragma unroll
           for (int k = 0; k < BKV / 16; ++k) {
-            // A: P, K-major, k-block (k / 4) of 64 keys, 32 bytes per 16 keys inside it.
-            const uint64_t a_desc =
-                make_smem_desc_sw128(p_addr + (k >> 2) * TILE_BYTES + (k & 3) * 32, 16, 1024);
+            // A: P in tensor memory, 16 keys = 8 columns (two 16-bit values per column).
             // B: V as loaded (key rows of 128 bytes): 16 keys = 2048 bytes further.
             const uint64_t b_desc = make_smem_desc_sw128(v_addr + k * 2048, 1024, 1024);
-            umma_f16_ss(tmem_base + O_COL, a_desc, b_desc, idesc_o, k != 0);
+            umma_f16_ts(tmem_base + O_COL, tmem_base + P_COL + k * 8, b_desc, idesc_o, k != 0);
           }
         }
         umma_commit(&bar_o_full);
         if (has_next) {
-          // V and P are free once this P.V has been computed
+          // V is free once this P.V has been computed
           if (!mbar_wait(&bar_o_full, ph, abort_flag)) { code = 0x52000000u | (t & 0xffff); break; }
           load_v(nxt, n_j);
         }
@@ -231,7 +234,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
       float o_acc[D];
 #pragma unroll
       for (int e = 0; e < D; ++e) o_acc[e] = 0.f;
-      float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+      float m_run = -INFINITY, l_run = 0.f;
       for (int j = 0; j < it.n_kv && ok; ++j, ++t) {
         const uint32_t ph = t & 1;
         if (!mbar_wait(&bar_s_full, ph, abort_flag)) {
@@ -259,25 +262,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
         // rows with no visible key yet keep m = -inf; use 0 as the reference point then
         const float m_ref = m_new == -INFINITY ? 0.f : m_new;
         const float alpha = m_run == -INFINITY ? 0.f : ex2_fast((m_run - m_ref) * p.scale_log2e);
-        // fold in the previous tile's partial product before P is overwritten
-        if (j > 0) {
-          if (!mbar_wait(&bar_o_full, ph ^ 1, abort_flag)) {
-            atomicCAS(p.err, 0u, 0x62000000u | (t & 0xffff));
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld_32x32(tmem_base + lane_addr + O_COL + c * 32, o);
-            tmem_ld_wait_regs(o);
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha_prev, __uint_as_float(o[i]));
-          }
-        }
-        // pass 2: P = exp2((s - m) * c), row sum, 16-bit P into swizzled shared memory
+        // pass 2: P = exp2((s - m) * c) and its row sum; the 16-bit P of keys [32c, 32c+32)
+        // goes to columns [16c, 16c+16), over S columns this thread has already consumed
         float l_tile = 0.f;
         const float mc = m_ref * p.scale_log2e;
 #pragma unroll 1
@@ -294,44 +280,32 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
             l_tile += p0 + p1;
             packed[i >> 1] = pack16<T16>(p0, p1);
           }
-          // 32 keys = four 16-byte chunks of row r in k-block (c / 2); chunk index is
-          // XOR-swizzled with the row (128-byte swizzle, same pattern TMA writes)
-          uint8_t *blk = sP + (c >> 1) * TILE_BYTES + r * 128;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int chunk = (c & 1) * 4 + q;
-            *reinterpret_cast<uint4 *>(blk + ((chunk ^ (r & 7)) << 4)) =
-                make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-          }
+          tmem_st_32x16(tmem_base + lane_addr + P_COL + c * 16, packed);
         }
         l_run = fmaf(l_run, alpha, l_tile);
         m_run = m_new;
-        alpha_prev = alpha;
-        // P visible to the tensor core (async proxy); S reads of this tile are complete
-        fence_proxy_async_smem();
+        // P is in tensor memory and every S column of this tile has been read
+        tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&bar_p_ready);
-      }
-      if (ok && it.n_kv > 0) {
-        // the last step of this item was t - 1
-        if (!mbar_wait(&bar_o_full, (t - 1) & 1, abort_flag)) {
-          atomicCAS(p.err, 0u, 0x63000000u);
+        // O_t = P.V of this tile: fold it into the running output, then hand the columns back
+        if (!mbar_wait(&bar_o_full, ph, abort_flag)) {
+          atomicCAS(p.err, 0u, 0x62000000u | (t & 0xffff));
           ok = false;
-        } else {
-          tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld_32x32(tmem_base + lane_addr + O_COL + c * 32, o);
-            tmem_ld_wait_regs(o);
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha_prev, __uint_as_float(o[i]));
-          }
-          // the O columns may be overwritten by the next step's P.V only after this read:
-          // that MMA is issued after the next bar_p_ready, which this thread has not given yet
-          tc_fence_before();
+          break;
         }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_base + lane_addr + O_COL + c * 32, o);
+          tmem_ld_wait_regs(o);
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha, __uint_as_float(o[i]));
+        }
+        tc_fence_before();
+        mbar_arrive(&bar_o_read);
       }
       if (ok && q_local < p.seq) {
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -399,8 +373,8 @@ MDC_API void mgpuAttention(const void *qkv, const int32_t *seq_lens, void *out, 
   p.err = err;
   const int64_t n_items = q_tiles * heads * batch;
   if (n_items > 0x7fffffff) { fail("mgpuAttention: shape too large"); return; }
-  // persistent CTAs, two per SM (80 KiB of shared memory and 256 TMEM columns each)
-  const int64_t slots = static_cast<int64_t>(di.sms) * 2;
+  // persistent CTAs, three per SM (49 KiB of shared memory and 128 TMEM columns each)
+  const int64_t slots = static_cast<int64_t>(di.sms) * attn::CTAS_PER_SM;
   dim3 grid(static_cast<unsigned>(n_items < slots ? n_items : slots));
   cudaStream_t s = as_stream(stream);
   ProfileScope prof(kCatAttention, s);
