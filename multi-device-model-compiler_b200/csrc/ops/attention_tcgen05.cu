@@ -380,7 +380,8 @@ MDC_API void mgpuAttention(const void *qkv, const int32_t *seq_lens, void *out, 
   ProfileScope prof(kCatAttention, s);
   if (dtype == MGPU_DTYPE_F16) {
     auto kern = attention_tcgen05_kernel<__half>;
-    static bool set = false;
+    static bool set_on[64] = {false};  // the attribute is per device
+    bool &set = set_on[(di.device >= 0 && di.device < 64) ? di.device : 0];
     if (!set) {
       if (!check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(attn::SMEM_BYTES)), "cudaFuncSetAttribute(attention)"))
@@ -390,7 +391,8 @@ MDC_API void mgpuAttention(const void *qkv, const int32_t *seq_lens, void *out, 
     check_cuda(launch_chain(kern, grid, dim3(attn::THREADS), attn::SMEM_BYTES, s, 1, tm, p), "launch attention");
   } else {
     auto kern = attention_tcgen05_kernel<__nv_bfloat16>;
-    static bool set = false;
+    static bool set_on[64] = {false};  // the attribute is per device
+    bool &set = set_on[(di.device >= 0 && di.device < 64) ? di.device : 0];
     if (!set) {
       if (!check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(attn::SMEM_BYTES)), "cudaFuncSetAttribute(attention)"))

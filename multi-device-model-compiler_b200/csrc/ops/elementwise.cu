@@ -49,9 +49,13 @@ void profile_mark(int category, cudaStream_t stream, bool begin) {
 
 const DeviceInfo &device_info() {
   static thread_local DeviceInfo info;
-  if (info.ok) return info;
   int dev = -1;
-  if (!check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return info;
+  if (!check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) {
+    info = DeviceInfo();
+    return info;
+  }
+  if (info.ok && info.device == dev) return info;  // cached for the thread's current device
+  info = DeviceInfo();
   cudaDeviceProp p;
   if (!check_cuda(cudaGetDeviceProperties(&p, dev), "cudaGetDeviceProperties")) return info;
   info.device = dev;

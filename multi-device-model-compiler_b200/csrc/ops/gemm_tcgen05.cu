@@ -593,14 +593,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #ifdef MDC_GEMM_TRACE
 static unsigned long long *g_gemm_trace = nullptr;
 #endif
-static uint32_t *g_err_slot = nullptr;
+// one status word per device ordinal (a process may drive several devices, one at a time)
+constexpr int kMaxDevices = 64;
+static uint32_t *g_err_slots[kMaxDevices] = {nullptr};
+static int current_device_index() {
+  const int d = device_info().device;
+  return (d >= 0 && d < kMaxDevices) ? d : 0;
+}
 
 uint32_t *device_error_slot() {
-  if (!g_err_slot) {
-    if (!check_cuda(cudaMalloc(&g_err_slot, sizeof(uint32_t)), "cudaMalloc(error slot)")) return nullptr;
-    check_cuda(cudaMemset(g_err_slot, 0, sizeof(uint32_t)), "cudaMemset(error slot)");
+  uint32_t *&slot = g_err_slots[current_device_index()];
+  if (!slot) {
+    if (!check_cuda(cudaMalloc(&slot, sizeof(uint32_t)), "cudaMalloc(error slot)")) return nullptr;
+    check_cuda(cudaMemset(slot, 0, sizeof(uint32_t)), "cudaMemset(error slot)");
   }
-  return g_err_slot;
+  return slot;
 }
 
 // elem: MGPU_DTYPE_*; swizzle_bytes: 128 or 64 (must equal box_inner * element size)
@@ -631,7 +638,8 @@ static void launch_gemm_cg(const CUtensorMap &ta, const CUtensorMap &tb, const C
                            const CUtensorMap &tr, const GemmParams &p, int grid, cudaStream_t s) {
   auto kern = gemm_tcgen05_kernel<T16, TOut, ACT, CG>;
   constexpr size_t smem = gemm::Cfg<CG>::SMEM_BYTES;
-  static bool attr_set = false;
+  static bool attr_set_on[kMaxDevices] = {false};  // the attribute is per device
+  bool &attr_set = attr_set_on[current_device_index()];
   if (!attr_set) {
     if (!check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
                     "cudaFuncSetAttribute(gemm)"))
@@ -910,7 +918,8 @@ MDC_API void mgpuMatmulNoAlloc(float *input, float *weight, float *bias, float *
   p.num_n_blocks = static_cast<int>((N + bn - 1) / bn);
   // the library's own status word if it exists already (so mgpuOpsCheckDeviceStatus sees a
   // kernel that gave up), else the word at the head of the fixed array
-  p.err = g_err_slot ? g_err_slot : status;
+  uint32_t *lib_slot = g_err_slots[current_device_index()];
+  p.err = lib_slot ? lib_slot : status;
 #ifdef MDC_GEMM_TRACE
   p.trace = nullptr;
 #endif
