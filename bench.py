@@ -285,6 +285,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--chunks", type=int, default=3, help="pipeline depth of the host-buffer (e2e) path")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--verbose", action="store_true", help="progress messages on stderr")
     ap.add_argument("--only-timed", action="store_true",
                     help="stop after the device-resident timed region (used for the ncu launch list)")
     args = ap.parse_args()
@@ -301,6 +302,10 @@ def main():
         run_micro(args)
         return
 
+    def note(msg):
+        if args.verbose:
+            print(f"[bench rank {rank}] {msg}", file=sys.stderr, flush=True)
+
     import __graft_entry__ as entry
     mdc = entry.load_package()
     dist = None
@@ -308,7 +313,20 @@ def main():
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        # NCCL prints its version banner on stdout when the communicator is created; stdout
+        # must carry the one JSON line only, so it points at stderr until NCCL is up
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            dist.barrier(device_ids=[local_rank])
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
+    note("process group up")
     mdc.init(local_rank)  # fails loudly without the CUDA libraries or a GPU
     rt, ops = mdc.runtime(), mdc.ops()
 
@@ -335,6 +353,7 @@ def main():
     def step():
         ops.mgpuEncoderStackRun(stack.h, dx.ptr, None, dy.ptr, B_PER_GPU, S, stream)
 
+    note("weights packed")
     # ---------------- device-resident timed region ----------------
     for _ in range(args.warmup):
         step()
@@ -364,6 +383,7 @@ def main():
         stack.close()
         return
 
+    note(f"timed region done: {ms_per_step:.3f} ms/step")
     # ---------------- per-kernel pass: Gemm launch durations ----------------
     ms_cat = (mdc.C.c_double * 4)()
     n_cat = (mdc.C.c_uint64 * 4)()
@@ -382,6 +402,7 @@ def main():
                 "time_share_per_step": {"gemm_ms": ms_cat[0] / args.steps, "attention_ms": ms_cat[1] / args.steps,
                                         "layernorm_ms": ms_cat[2] / args.steps, "cast_ms": ms_cat[3] / args.steps}}
 
+    note("per-kernel pass done")
     # ---------------- end to end through host buffers ----------------
     y_host = np.empty_like(x)
     rt.mgpuMemHostRegister(x.ctypes.data, x.nbytes)
@@ -404,6 +425,7 @@ def main():
            "h2d_bytes_per_step": int(x.nbytes), "d2h_bytes_per_step": int(y_host.nbytes),
            "ms_per_step": e2e_ms / args.steps, "chunks": args.chunks}
 
+    note("e2e done")
     # ---------------- HBM-bound kernels of the metric: LayerNorm and Add ----------------
     hbm = {}
     if rank == 0:
@@ -446,6 +468,7 @@ def main():
                "sample": f"{sample} of 256 sequences x 12 layers, once ({dt:.1f} s)",
                "parity_max_rel_vs_gpu": oracle.max_rel_err(ref, got, floor_frac=1.0)}
 
+    note("printing")
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
