@@ -102,6 +102,15 @@ void mgpuClearLastError(void);
 /* Lets the op library report its own failures through the same status. */
 void mgpuSetLastError(int32_t code, const char *what);
 
+/* Constant-weight cache.  A lowered graph re-uploads its weights with mgpuMemcpy on every
+ * call (lib/Dialect/Device/Transform/DeviceDataCopyGeneration.cpp:26-70).  After
+ * mgpuRegisterConstant(p, n) the caller promises not to change host bytes [p, p+n); the first
+ * mgpuMemcpy whose source is exactly p uploads them once into a device-resident copy and this
+ * and every later such copy is served device-to-device.  Unregister before freeing or
+ * changing the buffer. */
+void mgpuRegisterConstant(void *hostPtr, uint64_t sizeBytes);
+void mgpuUnregisterConstant(void *hostPtr);
+
 /* Pool introspection / control: bytes held from the driver, bytes handed out, and a call
  * that returns every cached block to the driver. */
 uint64_t mgpuPoolReservedBytes(void);

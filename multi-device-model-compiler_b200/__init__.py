@@ -79,6 +79,8 @@ RUNTIME_SIGNATURES = {
     "mgpuGetLastErrorString": (C.c_char_p, []),
     "mgpuClearLastError": (None, []),
     "mgpuSetLastError": (None, [_i32, C.c_char_p]),
+    "mgpuRegisterConstant": (None, [_vp, _u64]),
+    "mgpuUnregisterConstant": (None, [_vp]),
     "mgpuPoolReservedBytes": (_u64, []),
     "mgpuPoolInUseBytes": (_u64, []),
     "mgpuPoolTrim": (None, []),

@@ -8,6 +8,8 @@
 // processes, one per GPU, every other input replicated; no collective runs inside the
 // graph and the only exchange is the final gather of output rows, done by each worker
 // writing its slice of the output file.  --json prints one machine-readable result line.
+// --constants treats every input after the first as model constants (weights): they are
+// registered with the runtime's constant cache, so re-runs upload them once.
 // --timeout SECONDS bounds how long the parent waits for a worker before it reports it.
 // --device cpu runs a graph that needs no GPU: no CUDA call is made and re-runs are timed
 // with the host clock, which is what the reference's multi-device-cpu-runner does
@@ -40,7 +42,7 @@ struct Options {
   std::string input = "3_640_640,3_640_640", output = "3_640_640";
   std::vector<std::string> data;
   int rerun = 0, gpus = 1, timeout_s = 600;
-  bool json = false, cpu = false;
+  bool json = false, cpu = false, constants = false;
 };
 
 bool take_value(int argc, char **argv, int &i, const char *name, std::string *out) {
@@ -78,6 +80,7 @@ bool parse(int argc, char **argv, Options *o) {
       continue;
     }
     if (std::string(argv[i]) == "--json") { o->json = true; continue; }
+    if (std::string(argv[i]) == "--constants") { o->constants = true; continue; }
     if (take_value(argc, argv, i, "device", &v)) {
       if (v != "cpu" && v != "gpu") { fprintf(stderr, "--device must be gpu or cpu\n"); return false; }
       o->cpu = v == "cpu";
@@ -148,6 +151,10 @@ WorkerResult run_worker(const Options &o, int rank, int world, int result_fd) {
       }
     params[0]->set_dim0(rows);
   }
+
+  if (o.constants && !o.cpu)
+    for (size_t i = n_out + 1; i < params.size(); ++i)
+      mgpuRegisterConstant(params[i]->data(), params[i]->GetNumElements() * sizeof(float));
 
   void *handle = LoadLibrary(o.lib);
   if (!handle) return finish(false);

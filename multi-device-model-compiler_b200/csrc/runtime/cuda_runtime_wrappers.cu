@@ -16,6 +16,8 @@
 #include <mutex>
 #include <string>
 #include <unordered_map>
+#include <unordered_set>
+#include <vector>
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -143,6 +145,27 @@ std::unordered_map<std::string, CUfunction> g_builtin_cache;
 std::unordered_map<CUfunction, int32_t> g_smem_limit;
 
 constexpr int kMaxDevices = 64;
+constexpr size_t kMaxParked = 64;
+struct ObjectCache {
+  std::vector<cudaStream_t> streams;
+  std::vector<cudaEvent_t> events;
+  std::unordered_set<cudaEvent_t> untimed;  // events created by mgpuEventCreate
+};
+ObjectCache g_object_caches[kMaxDevices];
+ObjectCache &object_cache() {
+  int d = g_default_device;
+  if (d < 0 || d >= kMaxDevices) d = 0;
+  return g_object_caches[d];
+}
+// Host buffers the caller declared immutable (model weights): a device-resident copy is
+// made at the first upload and later uploads become device-to-device copies.
+struct Constant {
+  uint64_t bytes = 0;
+  int device = 0;
+  void *dev = nullptr;
+  cudaEvent_t uploaded = nullptr;
+};
+std::unordered_map<const void *, Constant> g_constants;
 mdc::DevicePool g_pools[kMaxDevices];
 mdc::DevicePool &pool() {
   int d = g_default_device;
@@ -274,13 +297,29 @@ MDC_API void mgpuBuiltinLaunchShape(int64_t n, intptr_t *gridX, intptr_t *blockX
 }
 
 // ---------------- streams / events ----------------
+// A lowered graph creates and destroys two streams and two events on every call
+// (lib/Dialect/Device/Transform/AsyncDependencyConvert.cpp:49-56,135-139).  Destroyed
+// objects are parked per device and handed out again: a parked stream may still have work
+// queued, which is harmless because whatever is submitted next is ordered behind it.
 MDC_API mgpu_stream_t mgpuStreamCreate(void) {
   if (!ensure_device()) return nullptr;
+  ObjectCache &c = object_cache();
+  if (!c.streams.empty()) {
+    cudaStream_t s = c.streams.back();
+    c.streams.pop_back();
+    return s;
+  }
   cudaStream_t s = nullptr;
   RT_CHECK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
   return s;
 }
 MDC_API void mgpuStreamDestroy(mgpu_stream_t stream) {
+  if (!stream) return;
+  ObjectCache &c = object_cache();
+  if (c.streams.size() < kMaxParked) {
+    c.streams.push_back(static_cast<cudaStream_t>(stream));
+    return;
+  }
   RT_CHECK(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
 }
 MDC_API void mgpuStreamSynchronize(mgpu_stream_t stream) {
@@ -291,8 +330,15 @@ MDC_API void mgpuStreamWaitEvent(mgpu_stream_t stream, mgpu_event_t event) {
 }
 MDC_API mgpu_event_t mgpuEventCreate(void) {
   if (!ensure_device()) return nullptr;
+  ObjectCache &c = object_cache();
+  if (!c.events.empty()) {
+    cudaEvent_t e = c.events.back();
+    c.events.pop_back();
+    return e;
+  }
   cudaEvent_t e = nullptr;
   RT_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  c.untimed.insert(e);
   return e;
 }
 MDC_API mgpu_event_t mgpuEventCreateWithStream(mgpu_stream_t /*stream*/) { return mgpuEventCreate(); }
@@ -303,7 +349,16 @@ MDC_API mgpu_event_t mgpuEventEnableTimeCreate(void) {
   return e;
 }
 MDC_API void mgpuEventDestroy(mgpu_event_t event) {
-  RT_CHECK(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+  if (!event) return;
+  ObjectCache &c = object_cache();
+  cudaEvent_t e = static_cast<cudaEvent_t>(event);
+  // only the plain (timing-disabled) events are parked; timing events are rare
+  if (c.untimed.count(e) && c.events.size() < kMaxParked) {
+    c.events.push_back(e);
+    return;
+  }
+  c.untimed.erase(e);
+  RT_CHECK(cudaEventDestroy(e));
 }
 MDC_API void mgpuEventSynchronize(mgpu_event_t event) {
   RT_CHECK(cudaEventSynchronize(static_cast<cudaEvent_t>(event)));
@@ -342,7 +397,48 @@ MDC_API void mgpuMemFreeAsync(void *ptr, mgpu_stream_t stream) { mgpuMemFree(ptr
 
 MDC_API void mgpuMemcpy(void *dst, void *src, size_t sizeBytes, mgpu_stream_t stream) {
   if (!ensure_device()) return;
-  RT_CHECK(cudaMemcpyAsync(dst, src, sizeBytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // a registered host constant (model weights): served from its device-resident copy
+  if (!g_constants.empty()) {
+    auto it = g_constants.find(src);
+    if (it != g_constants.end() && sizeBytes <= it->second.bytes && it->second.device == g_default_device) {
+      Constant &c = it->second;
+      if (!c.dev) {
+        cudaError_t e;
+        c.dev = pool().alloc(c.bytes, s, &e);
+        if (c.dev && RT_CHECK(cudaMemcpyAsync(c.dev, src, c.bytes, cudaMemcpyHostToDevice, s)))
+          RT_CHECK(cudaEventRecord(c.uploaded, s));
+      } else {
+        RT_CHECK(cudaStreamWaitEvent(s, c.uploaded, 0));
+      }
+      if (c.dev) {
+        RT_CHECK(cudaMemcpyAsync(dst, c.dev, sizeBytes, cudaMemcpyDeviceToDevice, s));
+        return;
+      }
+    }
+  }
+  RT_CHECK(cudaMemcpyAsync(dst, src, sizeBytes, cudaMemcpyDefault, s));
+}
+
+MDC_API void mgpuRegisterConstant(void *hostPtr, uint64_t sizeBytes) {
+  if (!hostPtr || !sizeBytes || !ensure_device()) return;
+  mgpuUnregisterConstant(hostPtr);
+  Constant c;
+  c.bytes = sizeBytes;
+  c.device = g_default_device;
+  if (!RT_CHECK(cudaEventCreateWithFlags(&c.uploaded, cudaEventDisableTiming))) return;
+  g_constants[hostPtr] = c;
+}
+
+MDC_API void mgpuUnregisterConstant(void *hostPtr) {
+  auto it = g_constants.find(hostPtr);
+  if (it == g_constants.end()) return;
+  if (it->second.dev) {
+    cudaError_t e;
+    pool().free(it->second.dev, nullptr, &e);
+  }
+  if (it->second.uploaded) cudaEventDestroy(it->second.uploaded);
+  g_constants.erase(it);
 }
 MDC_API void mgpuMemset32(void *dst, unsigned int value, size_t count, mgpu_stream_t stream) {
   if (!ensure_device() || !driver().ok) return;

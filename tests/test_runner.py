@@ -205,3 +205,27 @@ def test_gpu_batch_sharding_over_two_devices(tmp_path):
     r2 = run(common + ["--out-data", two, "--gpus", "2", "--rerun", "2", "--json"])
     assert r2.returncode == 0, r2.stderr + r2.stdout
     assert np.array_equal(np.fromfile(one, np.float32), np.fromfile(two, np.float32))
+
+
+@pytest.mark.gpu
+def test_gpu_gemm_config_with_constant_cache(tmp_path):
+    # the Gemm config (A [2048,4096], W [4096,4096] passed as [K,N], bias [4096]) through the
+    # runner; with --constants the weights are uploaded once and re-runs get faster, with the
+    # same bytes out
+    import json
+    rng = np.random.default_rng(7)
+    a = rng.standard_normal((2048, 4096)).astype(np.float32)
+    w = (0.02 * rng.standard_normal((4096, 4096))).astype(np.float32)
+    b = (0.02 * rng.standard_normal(4096)).astype(np.float32)
+    common = [os.path.join(PKG, "lib", "graph_gemm.so"), "--input", "2048_4096,4096_4096,4096", "--output", "2048_4096",
+              "--data", files(tmp_path, [a, w, b]), "--rerun", "5", "--json"]
+    plain, cached = str(tmp_path / "p.dat"), str(tmp_path / "c.dat")
+    r1 = run(common + ["--out-data", plain])
+    r2 = run(common + ["--out-data", cached, "--constants"])
+    assert r1.returncode == 0 and r2.returncode == 0, r1.stderr + r2.stderr
+    assert np.array_equal(np.fromfile(plain, np.float32), np.fromfile(cached, np.float32))
+    ref = oracle.matmul(a, w, b, round_mode=oracle.ROUND_F16)
+    assert oracle.max_rel_err(ref, np.fromfile(cached, np.float32).reshape(2048, 4096)) <= 2e-2
+    t1 = json.loads(r1.stdout.strip().splitlines()[-1])["avg_ms"]
+    t2 = json.loads(r2.stdout.strip().splitlines()[-1])["avg_ms"]
+    assert t2 < t1, (t1, t2)
