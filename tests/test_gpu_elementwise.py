@@ -121,3 +121,23 @@ def test_layernorm_16bit_with_residual(m, dtype_name, n):
     # 16-bit in, fp32 out (the last LayerNorm of a post-LN stack)
     y32 = m.layernorm(m.encode16(x, dt), g, b, 1e-5, io_dtype=dt, out_dtype=m.F32)
     assert np.max(np.abs(y32 - oracle.layernorm(x, g, b, 1e-5))) <= 1e-5
+
+
+@pytest.mark.parametrize("rows,n", [(4096, 768), (3001, 1024), (2051, 1536), (40000, 72)])
+@pytest.mark.parametrize("dtype_name", ["f16", "bf16"])
+def test_layernorm_16bit_large(m, rows, n, dtype_name):
+    # sizes that take the shared-memory ring kernel (rows staged by bulk copies), including
+    # a last group that is only partly filled
+    dt = m.F16 if dtype_name == "f16" else m.BF16
+    rm = oracle.ROUND_F16 if dt == m.F16 else oracle.ROUND_BF16
+    rng = np.random.default_rng(11)
+    x = oracle.round_array((2.0 * rng.standard_normal((rows, n)) + 0.5).astype(np.float32), rm)
+    g = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+    b = (0.1 * rng.standard_normal(n)).astype(np.float32)
+    ref = oracle.layernorm(x, g, b, 1e-5)
+    y32 = m.layernorm(m.encode16(x, dt), g, b, 1e-5, io_dtype=dt, out_dtype=m.F32)
+    assert np.max(np.abs(y32 - ref)) <= 1e-5
+    y16 = m.decode16(m.layernorm(m.encode16(x, dt), g, b, 1e-5, io_dtype=dt, out_dtype=dt), dt)
+    tol = 2 ** -9 if dt == m.F16 else 2 ** -6  # one output ulp at |y| < 8
+    assert np.max(np.abs(y16 - ref)) <= tol
+    assert m.ops().mgpuOpsCheckDeviceStatus(None) == 0
