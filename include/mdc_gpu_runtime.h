@@ -11,6 +11,12 @@
  * Differences from the reference that a caller can observe:
  *  - mgpuMemAlloc / mgpuMemFree are served by a caching, stream-ordered device pool
  *    instead of a synchronous cuMemAlloc / cuMemFree per call.
+ *  - mgpuMemcpy between pageable host memory and the device, 1 MiB and larger, is cut into
+ *    4 MiB chunks that a small team of host threads moves through a ring of pinned buffers
+ *    while the copy engine transfers the previous chunk (MDC_COPY_THREADS sets the team
+ *    size, MDC_STAGED_COPY=0 restores the plain cuMemcpyAsync).  Completion semantics are
+ *    those of a pageable copy: an upload returns once the source has been read, a download
+ *    is complete on return.
  *  - mgpuModuleGetFunction first looks the name up in a registry of built-in hand-written
  *    kernels (mdc_add_f32, ...) and only then in the module loaded from a file.
  *  - Errors never abort or throw: they are printed to stderr like the reference does and

@@ -13,8 +13,10 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <condition_variable>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <unordered_map>
 #include <unordered_set>
 #include <vector>
@@ -171,6 +173,182 @@ mdc::DevicePool &pool() {
   int d = g_default_device;
   if (d < 0 || d >= kMaxDevices) d = 0;
   return g_pools[d];
+}
+
+
+// ---- staged copies between pageable host memory and the device ----
+// cudaMemcpyAsync on pageable memory goes through the driver's single-threaded bounce
+// buffer.  Large copies are instead cut into chunks that a small team of host threads moves
+// into / out of a ring of pinned buffers while the copy engine works on the previous chunk.
+class CopyTeam {
+ public:
+  explicit CopyTeam(int helpers) {
+    for (int i = 0; i < helpers; ++i) std::thread([this, i] { work(i); }).detach();
+    helpers_ = helpers;
+  }
+  // memcpy(dst, src, n) split over the helpers and the calling thread
+  void copy(char *dst, const char *src, size_t n) {
+    const int parts = helpers_ + 1;
+    if (helpers_ == 0 || n < (size_t(256) << 10)) {
+      memcpy(dst, src, n);
+      return;
+    }
+    const size_t per = ((n + parts - 1) / parts + 63) & ~size_t(63);
+    {
+      std::lock_guard<std::mutex> lock(mu_);
+      dst_ = dst, src_ = src, n_ = n, per_ = per;
+      pending_ = helpers_;
+      ++generation_;
+    }
+    wake_.notify_all();
+    if (per * helpers_ < n) memcpy(dst + per * helpers_, src + per * helpers_, n - per * helpers_);
+    std::unique_lock<std::mutex> lock(mu_);
+    done_.wait(lock, [this] { return pending_ == 0; });
+  }
+
+ private:
+  void work(int index) {
+    uint64_t seen = 0;
+    for (;;) {
+      char *dst;
+      const char *src;
+      size_t n, per;
+      {
+        std::unique_lock<std::mutex> lock(mu_);
+        wake_.wait(lock, [&] { return generation_ != seen; });
+        seen = generation_;
+        dst = dst_, src = src_, n = n_, per = per_;
+      }
+      const size_t begin = per * index;
+      if (begin < n) memcpy(dst + begin, src + begin, (n - begin < per) ? n - begin : per);
+      std::lock_guard<std::mutex> lock(mu_);
+      if (--pending_ == 0) done_.notify_one();
+    }
+  }
+  std::mutex mu_;
+  std::condition_variable wake_, done_;
+  char *dst_ = nullptr;
+  const char *src_ = nullptr;
+  size_t n_ = 0, per_ = 0;
+  int pending_ = 0, helpers_ = 0;
+  uint64_t generation_ = 0;
+};
+
+CopyTeam &copy_team() {
+  // never destroyed: its helper threads may still be parked when the process exits
+  static CopyTeam *team = [] {
+    // measured on a 16-core host, 256 MiB: upload 11 GB/s through the driver's own path,
+    // 12 / 21 / 30 / 43 GB/s with 1 / 2 / 4 / 8 threads; download 18 vs 9 / 16 / 17 / 28
+    const int hw = static_cast<int>(std::thread::hardware_concurrency());
+    int threads = hw >= 16 ? 8 : (hw >= 2 ? hw / 2 : 1);
+    if (const char *e = getenv("MDC_COPY_THREADS")) threads = atoi(e);
+    if (hw > 0 && threads > hw) threads = hw;
+    if (threads < 1) threads = 1;
+    return new CopyTeam(threads - 1);
+  }();
+  return *team;
+}
+
+constexpr size_t kStageChunk = size_t(4) << 20;
+constexpr size_t kStageThreshold = size_t(1) << 20;  // smaller copies take the plain path
+constexpr int kStageSlots = 4;
+struct StagingRing {
+  char *slot[kStageSlots] = {};
+  cudaEvent_t done[kStageSlots] = {};
+  bool busy[kStageSlots] = {};
+  bool ready = false, failed = false;
+};
+StagingRing g_staging[kMaxDevices];
+
+StagingRing *staging_ring() {
+  static const bool off = getenv("MDC_STAGED_COPY") && atoi(getenv("MDC_STAGED_COPY")) == 0;
+  if (off) return nullptr;
+  int d = g_default_device;
+  if (d < 0 || d >= kMaxDevices) d = 0;
+  StagingRing &r = g_staging[d];
+  if (r.failed) return nullptr;
+  if (!r.ready) {
+    for (int i = 0; i < kStageSlots; ++i) {
+      if (cudaHostAlloc(reinterpret_cast<void **>(&r.slot[i]), kStageChunk, cudaHostAllocDefault) != cudaSuccess ||
+          cudaEventCreateWithFlags(&r.done[i], cudaEventDisableTiming) != cudaSuccess) {
+        (void)cudaGetLastError();
+        r.failed = true;  // the plain path still works
+        return nullptr;
+      }
+    }
+    r.ready = true;
+  }
+  return &r;
+}
+
+enum class MemKind { PageableHost, PinnedHost, Device, Unknown };
+MemKind mem_kind(const void *p) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return MemKind::Unknown;
+  }
+  switch (attr.type) {
+    case cudaMemoryTypeUnregistered: return MemKind::PageableHost;
+    case cudaMemoryTypeHost: return MemKind::PinnedHost;
+    case cudaMemoryTypeDevice: return MemKind::Device;
+    default: return MemKind::Unknown;  // managed memory: leave it to the driver
+  }
+}
+
+// Returns true when the copy was carried out (or failed and was reported) here.
+bool staged_copy(void *dst, const void *src, size_t bytes, cudaStream_t s) {
+  if (bytes < kStageThreshold) return false;
+  cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(s, &capture) != cudaSuccess || capture != cudaStreamCaptureStatusNone) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  const MemKind sk = mem_kind(src), dk = mem_kind(dst);
+  const bool up = sk == MemKind::PageableHost && dk == MemKind::Device;
+  const bool down = sk == MemKind::Device && dk == MemKind::PageableHost;
+  if (!up && !down) return false;
+  StagingRing *ring = staging_ring();
+  if (!ring) return false;
+  CopyTeam &team = copy_team();
+  const size_t chunks = (bytes + kStageChunk - 1) / kStageChunk;
+  auto span = [&](size_t c) { return (c + 1 == chunks) ? bytes - c * kStageChunk : kStageChunk; };
+  if (up) {
+    // like the driver's pageable path: returns once the source has been read, not once it
+    // has arrived
+    for (size_t c = 0; c < chunks; ++c) {
+      const int i = static_cast<int>(c % kStageSlots);
+      if (ring->busy[i] && !RT_CHECK(cudaEventSynchronize(ring->done[i]))) return true;
+      team.copy(ring->slot[i], static_cast<const char *>(src) + c * kStageChunk, span(c));
+      if (!RT_CHECK(cudaMemcpyAsync(static_cast<char *>(dst) + c * kStageChunk, ring->slot[i], span(c),
+                                    cudaMemcpyHostToDevice, s)) ||
+          !RT_CHECK(cudaEventRecord(ring->done[i], s)))
+        return true;
+      ring->busy[i] = true;
+    }
+    return true;
+  }
+  // download: keep the copy engine kStageSlots chunks ahead of the host threads; complete on
+  // return, as a copy into pageable memory is
+  for (int i = 0; i < kStageSlots; ++i)
+    if (ring->busy[i]) {
+      if (!RT_CHECK(cudaEventSynchronize(ring->done[i]))) return true;
+      ring->busy[i] = false;
+    }
+  size_t issued = 0;
+  for (size_t c = 0; c < chunks; ++c) {
+    for (; issued < chunks && issued < c + kStageSlots; ++issued) {
+      const int j = static_cast<int>(issued % kStageSlots);
+      if (!RT_CHECK(cudaMemcpyAsync(ring->slot[j], static_cast<const char *>(src) + issued * kStageChunk,
+                                    span(issued), cudaMemcpyDeviceToHost, s)) ||
+          !RT_CHECK(cudaEventRecord(ring->done[j], s)))
+        return true;
+    }
+    const int i = static_cast<int>(c % kStageSlots);
+    if (!RT_CHECK(cudaEventSynchronize(ring->done[i]))) return true;
+    team.copy(static_cast<char *>(dst) + c * kStageChunk, ring->slot[i], span(c));
+  }
+  return true;
 }
 
 int num_sms() {
@@ -417,6 +595,7 @@ MDC_API void mgpuMemcpy(void *dst, void *src, size_t sizeBytes, mgpu_stream_t st
       }
     }
   }
+  if (staged_copy(dst, src, sizeBytes, s)) return;
   RT_CHECK(cudaMemcpyAsync(dst, src, sizeBytes, cudaMemcpyDefault, s));
 }
 
