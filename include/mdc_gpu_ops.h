@@ -37,9 +37,16 @@ enum { MGPU_ACT_NONE = 0, MGPU_ACT_RELU = 1, MGPU_ACT_GELU_ERF = 2, MGPU_ACT_GEL
 void mgpuMatmul(float *input, float *weight, float *bias, float *output, int64_t M, int64_t N,
                 int64_t K, mgpu_cuda_stream_t stream);
 
-/* Ops.h:27-34 / Ops.cu:238-340 and Ops.h:36-42 / Ops.cu:342-374.  CNN ops are outside the
- * transformer path this library serves: the symbols exist so lowered graphs link, and a
- * call sets the status to "not implemented". */
+/* Ops.h:27-34 / Ops.cu:238-340 and Ops.h:36-42 / Ops.cu:342-374 (CPU twins
+ * lib/Kernels/CPU/Ops.cpp:83-210).  fp32 NCHW device tensors, OIHW filter, bias [OC];
+ * paddings top / left / bottom / right = PHL / PWL / PHR / PWR (all four honoured), strides
+ * SH / SW, ONNX dilations DH / DW; OH / OW are the caller's output extents and must fit the
+ * padded input.  output = conv(input, weight) + bias (+ postAdd if hasPostAdd) with ReLU last
+ * if hasContainRelu; the filter is applied as a cross-correlation (ONNX Conv and the
+ * reference's CPU path; its GPU path requests cuDNN's flipped-filter mode, Ops.cu:258).
+ * Operands are rounded to fp16 for the tensor cores, accumulation is fp32.
+ * mgpuPool2d: method 0 = max, 1 = average with the padding counted in the divisor.
+ * Bad geometry sets the status and launches nothing. */
 void mgpuConv2d(float *input, float *weight, float *bias, float *output, float *postAdd, int64_t N,
                 int64_t IC, int64_t H, int64_t W, int64_t OC, int64_t KH, int64_t KW, int64_t OH,
                 int64_t OW, int64_t PHL, int64_t PWL, int64_t PHR, int64_t PWR, int64_t SH,

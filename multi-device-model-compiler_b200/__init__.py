@@ -282,6 +282,44 @@ def cast(x: np.ndarray, src: int, dst: int) -> np.ndarray:
     return out
 
 
+def conv2d(x, w, bias, post_add=None, stride=(1, 1), pad=(0, 0, 0, 0), dilation=(1, 1), relu=False):
+    """mgpuConv2d on numpy arrays: x [N,IC,H,W], w [OC,IC,KH,KW], pad = (top, left, bottom, right)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    bias = np.ascontiguousarray(bias, dtype=np.float32)
+    N, IC, H, W = x.shape
+    OC, _, KH, KW = w.shape
+    OH = (H + pad[0] + pad[2] - (KH - 1) * dilation[0] - 1) // stride[0] + 1
+    OW = (W + pad[1] + pad[3] - (KW - 1) * dilation[1] - 1) // stride[1] + 1
+    dx, dw, db = to_device(x), to_device(w), to_device(bias)
+    dp = to_device(np.ascontiguousarray(post_add, dtype=np.float32)) if post_add is not None else None
+    dy = DeviceBuffer(N * OC * OH * OW * 4)
+    ops().mgpuConv2d(dx.ptr, dw.ptr, db.ptr, dy.ptr, dp.ptr if dp else None, N, IC, H, W, OC, KH, KW, OH, OW,
+                     pad[0], pad[1], pad[2], pad[3], stride[0], stride[1], dilation[0], dilation[1],
+                     post_add is not None, bool(relu), None)
+    out = to_host(dy, (N, OC, OH, OW), np.float32)
+    status = ops().mgpuOpsCheckDeviceStatus(None)
+    check("mgpuConv2d")
+    if status:
+        raise MdcError(f"device status 0x{status:08x}")
+    return out
+
+
+def pool2d(x, kernel, stride, pad=(0, 0, 0, 0), method=0):
+    """mgpuPool2d on a numpy array [N,C,H,W]; method 0 = max, 1 = average with the padding counted."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    N, Cc, H, W = x.shape
+    OH = (H + pad[0] + pad[2] - kernel[0]) // stride[0] + 1
+    OW = (W + pad[1] + pad[3] - kernel[1]) // stride[1] + 1
+    dx = to_device(x)
+    dy = DeviceBuffer(N * Cc * OH * OW * 4)
+    ops().mgpuPool2d(dx.ptr, dy.ptr, N, Cc, H, W, OH, OW, kernel[0], kernel[1], pad[0], pad[1], pad[2], pad[3],
+                     stride[0], stride[1], method, None)
+    out = to_host(dy, (N, Cc, OH, OW), np.float32)
+    check("mgpuPool2d")
+    return out
+
+
 def layernorm(x, gamma=None, beta=None, eps=1e-5, residual=None, io_dtype=F32, out_dtype=F32,
               return_sum=False):
     """x / residual are storage arrays of io_dtype; returns the storage array of out_dtype."""

@@ -1,5 +1,5 @@
 // Library lifetime (gpuOpsInit / gpuOpsDeinit), the reference's mgpuMatmul entry point on
-// top of the tensor-core Gemm, and the CNN symbols that only exist so lowered graphs link.
+// top of the tensor-core Gemm.
 #include "ops_common.h"
 
 namespace mdc {
@@ -47,15 +47,4 @@ MDC_API void mgpuMatmul(float *input, float *weight, float *bias, float *output,
   }
   if (a16) mgpuMemFreeAsync(a16, stream);
   if (w16) mgpuMemFreeAsync(w16, stream);
-}
-
-// ---- CNN ops: outside the transformer path ----
-MDC_API void mgpuConv2d(float *, float *, float *, float *, float *, int64_t, int64_t, int64_t, int64_t,
-                        int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
-                        int64_t, int64_t, int64_t, int64_t, bool, bool, void *) {
-  fail("mgpuConv2d is not implemented in this library");
-}
-MDC_API void mgpuPool2d(float *, float *, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
-                        int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, void *) {
-  fail("mgpuPool2d is not implemented in this library");
 }

@@ -130,6 +130,41 @@ def layernorm(x, gamma=None, beta=None, eps=1e-5, residual=None, sum_round=ROUND
     return (y, s) if return_sum else y
 
 
+def conv2d(x, w, bias=None, post_add=None, stride=(1, 1), pad=(0, 0, 0, 0), dilation=(1, 1),
+           relu=False, round_mode=ROUND_NONE, accum64=False):
+    """x [N,IC,H,W], w [OC,IC,KH,KW]; pad = (top, left, bottom, right)."""
+    x, px = _f(x)
+    w, pw = _f(w)
+    bias, pb = _fo(bias)
+    post_add, pp = _fo(post_add)
+    N, IC, H, W = x.shape
+    OC, _, KH, KW = w.shape
+    OH = (H + pad[0] + pad[2] - (KH - 1) * dilation[0] - 1) // stride[0] + 1
+    OW = (W + pad[1] + pad[3] - (KW - 1) * dilation[1] - 1) // stride[1] + 1
+    out = np.empty((N, OC, OH, OW), dtype=np.float32)
+    i64 = C.c_int64
+    lib().oracle_conv2d(px, pw, pb, pp, out.ctypes.data_as(_fp), i64(N), i64(IC), i64(H), i64(W),
+                        i64(OC), i64(KH), i64(KW), i64(OH), i64(OW), i64(pad[0]), i64(pad[1]),
+                        i64(stride[0]), i64(stride[1]), i64(dilation[0]), i64(dilation[1]),
+                        C.c_int(int(post_add is not None)), C.c_int(int(relu)), C.c_int(round_mode),
+                        C.c_int(int(accum64)))
+    return out
+
+
+def pool2d(x, kernel, stride, pad=(0, 0, 0, 0), method=0):
+    """x [N,C,H,W]; pad = (top, left, bottom, right); method 0 = max, 1 = average (padding counted)."""
+    x, px = _f(x)
+    N, Cc, H, W = x.shape
+    OH = (H + pad[0] + pad[2] - kernel[0]) // stride[0] + 1
+    OW = (W + pad[1] + pad[3] - kernel[1]) // stride[1] + 1
+    out = np.empty((N, Cc, OH, OW), dtype=np.float32)
+    i64 = C.c_int64
+    lib().oracle_pool2d(px, out.ctypes.data_as(_fp), i64(N), i64(Cc), i64(H), i64(W), i64(OH), i64(OW),
+                        i64(kernel[0]), i64(kernel[1]), i64(pad[0]), i64(pad[1]), i64(pad[2]), i64(pad[3]),
+                        i64(stride[0]), i64(stride[1]), C.c_int(method))
+    return out
+
+
 def attention(qkv, seq_lens, B, S, H, D, causal=False, round_mode=ROUND_NONE):
     """qkv: [B*S, 3, H, D] packed per token; returns [B*S, H*D]."""
     qkv, pq = _f(qkv)

@@ -37,3 +37,9 @@ def mdc():
 def golden():
     import numpy as np
     return np.load(os.path.join(ROOT, "tests", "golden", "reference_models.npz"))
+
+
+@pytest.fixture(scope="session")
+def golden_cnn():
+    import numpy as np
+    return np.load(os.path.join(ROOT, "tests", "golden", "reference_cnn.npz"))

@@ -108,6 +108,50 @@ def main(ref_root: str):
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_models.npz")
     np.savez_compressed(dst, **out)
     print("wrote", dst, os.path.getsize(dst), "bytes")
+    cnn_fixtures()
+
+
+def cnn_fixtures():
+    """Conv2d / Pool2d fixtures -> reference_cnn.npz (own seed, so the file above never changes)."""
+    from Models import Conv, MaxPool  # the reference's model files
+    import torch.nn.functional as F
+
+    torch.manual_seed(20240301)
+    out = {}
+    # --- reference Conv(3, 64): 3x3, stride 1, padding 1 (test/End2End/GPU/conv.mlir's layer) ---
+    conv = Conv.Conv(3, 64).eval()
+    with torch.no_grad():
+        x = torch.randn(2, 3, 20, 24)
+        y = conv(x)
+    out["conv_x"], out["conv_y"] = x.numpy(), y.numpy()
+    out["conv_w"] = conv.conv.weight.detach().numpy().copy()
+    out["conv_b"] = conv.conv.bias.detach().numpy().copy()
+    # --- reference MaxPool(): 4x4 window, stride 4 (test/End2End/GPU/pool.mlir's layer) ---
+    with torch.no_grad():
+        x = torch.randn(2, 3, 16, 24)
+        y = MaxPool.MaxPool().eval()(x)
+    out["maxpool_x"], out["maxpool_y"] = x.numpy(), y.numpy()
+    # --- cross-checks (NOT reference code) ---
+    with torch.no_grad():
+        # residual block tail: relu(conv(x) + b + identity), stride 2, padding 1
+        x, w, b = torch.randn(2, 8, 15, 17), 0.2 * torch.randn(16, 8, 3, 3), 0.1 * torch.randn(16)
+        y0 = F.conv2d(x, w, b, stride=2, padding=1)
+        add = torch.randn_like(y0)
+        out["res_x"], out["res_w"], out["res_b"], out["res_add"] = x.numpy(), w.numpy(), b.numpy(), add.numpy()
+        out["res_y"] = torch.relu(y0 + add).numpy()
+        # dilation 2, rectangular filter, no padding
+        x, w, b = torch.randn(1, 5, 14, 19), 0.2 * torch.randn(7, 5, 3, 2), 0.1 * torch.randn(7)
+        out["dil_x"], out["dil_w"], out["dil_b"] = x.numpy(), w.numpy(), b.numpy()
+        out["dil_y"] = F.conv2d(x, w, b, stride=(1, 2), dilation=(2, 3)).numpy()
+        # pooling: the ResNet stem's 3x3 / stride 2 / padding 1 max pool, and an average pool
+        # that counts its padding
+        x = torch.randn(2, 4, 13, 18)
+        out["pool_x"] = x.numpy()
+        out["pool_max_y"] = F.max_pool2d(x, 3, 2, 1).numpy()
+        out["pool_avg_y"] = F.avg_pool2d(x, 3, 2, 1, count_include_pad=True).numpy()
+    dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_cnn.npz")
+    np.savez_compressed(dst, **out)
+    print("wrote", dst, os.path.getsize(dst), "bytes")
 
 
 if __name__ == "__main__":

@@ -70,12 +70,19 @@ def test_no_cpu_fallback_without_a_gpu(built):
     rt.mgpuClearLastError()
 
 
-def test_unimplemented_cnn_ops_set_the_status(built):
+def test_cnn_ops_reject_bad_geometry_before_touching_a_device(built):
     rt, ops = built.runtime(), built.ops()
     rt.mgpuClearLastError()
-    ops.mgpuPool2d(None, None, *([1] * 15), None)
+    # N, C, H, W, OH, OW, KH, KW, PHL, PWL, PHR, PWR, SH, SW, method: stride 0
+    ops.mgpuPool2d(None, None, 1, 1, 4, 4, 2, 2, 2, 2, 0, 0, 0, 0, 0, 2, 0, None)
     assert rt.mgpuGetLastError() != 0
     assert b"mgpuPool2d" in rt.mgpuGetLastErrorString()
+    rt.mgpuClearLastError()
+    # output extent larger than the padded input allows
+    ops.mgpuConv2d(None, None, None, None, None, 1, 3, 8, 8, 4, 3, 3, 9, 9, 0, 0, 0, 0, 1, 1, 1, 1,
+                   False, False, None)
+    assert rt.mgpuGetLastError() != 0
+    assert b"mgpuConv2d" in rt.mgpuGetLastErrorString()
     rt.mgpuClearLastError()
     assert rt.mgpuGetLastError() == 0
 

@@ -101,3 +101,37 @@ def test_attention_masks():
     # causal: first row attends only to itself
     outc = oracle.attention(qkv, lens, B, S, H, D, causal=True)
     assert np.allclose(outc.reshape(B, S, H, D)[0, 0], v[0, 0], atol=1e-6)
+
+
+def test_reference_conv_layer(golden_cnn):
+    # benchmark/PyTorch/Models/Conv.py: Conv2d(3, 64, 3, 1, 1), the layer of test/End2End/GPU/conv.mlir
+    g = golden_cnn
+    y = oracle.conv2d(g["conv_x"], g["conv_w"], g["conv_b"], pad=(1, 1, 1, 1))
+    assert y.shape == g["conv_y"].shape
+    assert np.max(np.abs(y - g["conv_y"])) <= 2e-5
+    y64 = oracle.conv2d(g["conv_x"], g["conv_w"], g["conv_b"], pad=(1, 1, 1, 1), accum64=True)
+    assert np.max(np.abs(y64 - g["conv_y"])) <= 2e-5
+
+
+def test_reference_maxpool_layer(golden_cnn):
+    # benchmark/PyTorch/Models/MaxPool.py: MaxPool2d(4), the layer of test/End2End/GPU/pool.mlir
+    g = golden_cnn
+    y = oracle.pool2d(g["maxpool_x"], (4, 4), (4, 4))
+    assert np.array_equal(y, g["maxpool_y"])
+
+
+def test_crosscheck_conv_variants(golden_cnn):
+    g = golden_cnn
+    y = oracle.conv2d(g["res_x"], g["res_w"], g["res_b"], post_add=g["res_add"], stride=(2, 2),
+                      pad=(1, 1, 1, 1), relu=True)
+    assert y.shape == g["res_y"].shape and np.max(np.abs(y - g["res_y"])) <= 2e-5
+    y = oracle.conv2d(g["dil_x"], g["dil_w"], g["dil_b"], stride=(1, 2), dilation=(2, 3))
+    assert y.shape == g["dil_y"].shape and np.max(np.abs(y - g["dil_y"])) <= 2e-5
+
+
+def test_crosscheck_pool_variants(golden_cnn):
+    g = golden_cnn
+    y = oracle.pool2d(g["pool_x"], (3, 3), (2, 2), pad=(1, 1, 1, 1), method=0)
+    assert np.array_equal(y, g["pool_max_y"])
+    y = oracle.pool2d(g["pool_x"], (3, 3), (2, 2), pad=(1, 1, 1, 1), method=1)
+    assert y.shape == g["pool_avg_y"].shape and np.max(np.abs(y - g["pool_avg_y"])) <= 1e-6
