@@ -183,6 +183,16 @@ MICRO = {
 }
 
 
+# Convolution layers for --micro: the reference's test layer and three ResNet-18 layers at
+# batch 32.  N, IC, H, W, OC, KH, KW, stride, padding
+CONV_MICRO = {
+    "conv_ref": (16, 3, 256, 256, 64, 3, 3, 1, 1),       # test/End2End/GPU/conv.mlir
+    "conv_stem": (32, 3, 224, 224, 64, 7, 7, 2, 3),
+    "conv_56": (32, 64, 56, 56, 64, 3, 3, 1, 1),
+    "conv_14": (32, 256, 14, 14, 256, 3, 3, 1, 1),
+}
+
+
 def run_micro(args):
     """One kernel, a few launches, on random data: the small case the ncu captures in
     profiles/ are taken on.  Prints one JSON line with the CUDA-event time per launch."""
@@ -256,6 +266,24 @@ def run_micro(args):
         else:
             fn = lambda: ops.mgpuAdd(a.ptr, b.ptr, c.ptr, rows * n, stream)
             work, unit = 3.0 * rows * n * 4, "GB/s"
+    elif name in CONV_MICRO:
+        # N, IC, H, W, OC, KH, KW, stride, padding (symmetric), relu
+        Nn, IC, Hh, Ww, OC, KH, KW, st, pd = CONV_MICRO[name]
+        OH, OW = (Hh + 2 * pd - KH) // st + 1, (Ww + 2 * pd - KW) // st + 1
+        x = mdc.to_device(rng.standard_normal((Nn, IC, Hh, Ww)).astype(np.float32), stream)
+        w = mdc.to_device((rng.standard_normal((OC, IC, KH, KW)) / np.sqrt(IC * KH * KW)).astype(np.float32), stream)
+        bias = mdc.to_device(np.zeros(OC, np.float32), stream)
+        out = mdc.DeviceBuffer(Nn * OC * OH * OW * 4, stream)
+        fn = lambda: ops.mgpuConv2d(x.ptr, w.ptr, bias.ptr, out.ptr, None, Nn, IC, Hh, Ww, OC, KH, KW, OH, OW,
+                                    pd, pd, pd, pd, st, st, 1, 1, False, True, stream)
+        work, unit = 2.0 * Nn * OH * OW * OC * IC * KH * KW, "TFLOP/s"
+    elif name == "maxpool_ref":
+        # test/End2End/GPU/pool.mlir scaled x8 in batch so the tensors exceed L2: 4x4 / stride 4
+        Nn, Cc, Hh, Ww = 128, 3, 256, 256
+        x = mdc.to_device(rng.standard_normal((Nn, Cc, Hh, Ww)).astype(np.float32), stream)
+        out = mdc.DeviceBuffer(Nn * Cc * 64 * 64 * 4, stream)
+        fn = lambda: ops.mgpuPool2d(x.ptr, out.ptr, Nn, Cc, Hh, Ww, 64, 64, 4, 4, 0, 0, 0, 0, 4, 4, 0, stream)
+        work, unit = Nn * Cc * (Hh * Ww + 64 * 64) * 4.0, "GB/s"
     else:
         raise SystemExit(f"unknown --micro {name}")
     for _ in range(args.warmup):
@@ -276,7 +304,8 @@ def run_micro(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--micro", default=None, help="run one kernel only (for profiling): " + ", ".join(
-        list(MICRO) + ["matmul_c1_abi", "layer_c3", "attention", "attention_c3", "layernorm_f32", "layernorm_f16", "add_f32"]))
+        list(MICRO) + ["matmul_c1_abi", "layer_c3", "attention", "attention_c3", "layernorm_f32", "layernorm_f16", "add_f32",
+                     "maxpool_ref"] + list(CONV_MICRO)))
     ap.add_argument("--tokens", type=int, default=8192, help="--micro: rows / tokens of the small case")
     ap.add_argument("--hidden", type=int, default=768, help="--micro layernorm_f32 / add_f32: row length")
     ap.add_argument("--gpus", type=int, default=1)

@@ -1,0 +1,398 @@
+// mgpuConv2d (reference: lib/Kernels/GPU/Ops.cu:238-340, CPU twin lib/Kernels/CPU/Ops.cpp:83-157)
+// as an implicit Gemm on the tcgen05 tensor cores: fp32 NCHW tensors and an OIHW filter at the
+// boundary, fp16 operands, fp32 accumulation in tensor memory.
+//
+//   out[n, oc, oh, ow] = sum_k  patch[(n, oh, ow), k] * filter[oc, k]
+// with k running over (ic, kh, kw) in an order chosen per shape (see the kernel's template flag).
+//
+// One CTA computes 128 output pixels x BN output channels.  The patch matrix is never
+// written to global memory:
+//   * warps 0-7 (two threads per pixel) gather the 64 k-values of their pixel per k-block
+//     straight from the NCHW input (a warp's 32 pixels are neighbours along ow, so every load
+//     is one coalesced line; all 32 loads of a thread are in flight together), convert them
+//     and store their half of the pixel's 128-byte row into shared memory in the
+//     128-byte-swizzle layout the tensor core reads; a proxy fence + mbarrier arrive hands the
+//     stage to the MMA thread;
+//   * warp 8 / lane 0 loads the matching 64 x BN block of the fp16 filter with TMA (plain tile
+//     load, 128-byte swizzle; the filter stays in L2);
+//   * warp 9 / lane 0 issues tcgen05.mma (M = 128, N = BN, K = 16, four per k-block) and commits
+//     each stage back to the producers;
+//   * warps 0-7 then read the accumulator (thread = pixel, registers = channels) and write
+//     NCHW directly: for a fixed channel a warp's 32 pixels are 128 contiguous bytes, so the
+//     stores are whole lines without a transpose.  Bias, postAdd and ReLU are applied here.
+// The filter is applied as a cross-correlation (ONNX Conv, oneDNN convolution_forward).
+// The reference's GPU path asks cuDNN for CUDNN_CONVOLUTION (a flipped filter, Ops.cu:258),
+// which disagrees with its own CPU path; this library follows the CPU path and ONNX.
+// With both flags set the result is relu(conv + bias + postAdd), cuDNN's fused form
+// (Ops.cu:334-337).
+#include <cuda_fp16.h>
+
+#include "ops_common.h"
+#include "ptx_sm100.cuh"
+
+namespace mdc {
+void cast_rows_padded(const float *src, void *dst, int64_t R, int64_t C, int64_t Cp, int32_t dtype,
+                      cudaStream_t s);
+bool encode_tmap_2d(CUtensorMap *map, const void *base, int32_t dtype, uint64_t inner, uint64_t outer,
+                    uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
+
+namespace conv {
+constexpr int BM = 128;          // output pixels per CTA
+constexpr int BK = 64;           // k-elements per stage: one 128-byte swizzled row
+constexpr int STAGES = 3;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int GATHER_WARPS = 8;  // two threads per pixel row
+constexpr int THREADS = (GATHER_WARPS + 2) * 32;  // + filter loader, MMA issuer
+
+struct Params {
+  const float *x, *bias, *add;
+  float *out;
+  int IC, H, W, OC, KH, KW, OH, OW, PHL, PWL, SH, SW, DH, DW;
+  int M, P, K, num_kb;  // pixels in total, pixels per image, IC*KH*KW, k-blocks
+  int bn;               // channels per CTA: 32, 64, 128 or 256
+  int relu;
+  uint32_t *err;
+};
+
+inline size_t smem_bytes(int bn) { return size_t(STAGES) * (A_BYTES + bn * BK * 2) + 1024; }
+}  // namespace conv
+
+// TAP_MAJOR (IC a multiple of 32): k = ((ic / 32) * KH*KW + kh*KW + kw) * 32 + ic % 32, so the
+// 32 k-values a gather thread handles share one filter tap (one bounds test, 32 loads a
+// channel plane apart) and consecutive k-blocks walk the taps of the same 32 channels, whose
+// input lines are then re-served by L1 instead of L2.
+// Otherwise k = (ic*KH + kh)*KW + kw (the filter's own order) and every element carries its
+// own tap arithmetic.
+template <bool TAP_MAJOR>
+__global__ void __launch_bounds__(conv::THREADS, 3)
+conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const conv::Params p) {
+  using namespace conv;
+  using namespace ptx;
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ uint32_t tmem_slot, abort_flag_s;
+  volatile uint32_t *abort_flag = &abort_flag_s;
+  uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bn = p.bn;
+  const int stage_bytes = A_BYTES + bn * BK * 2;
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * bn;
+
+  if (threadIdx.x == 0) {
+    abort_flag_s = 0;
+    tma_prefetch_desc(&tmap_w);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], GATHER_WARPS + 1);  // one arrive per gather warp + the filter loader's expect_tx
+      mbar_init(&empty_bar[s], 1);      // one tcgen05.commit
+    }
+    mbar_init(&acc_bar, 1);
+    mbar_init_fence();
+  }
+  if (warp == GATHER_WARPS) {
+    tmem_alloc(&tmem_slot, static_cast<uint32_t>(bn));
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  pdl_wait();
+
+  if (warp < GATHER_WARPS) {
+    // ---------------- gather: two threads per output pixel, 32 k-values each ----------------
+    const int row = threadIdx.x & (BM - 1);
+    const int half = threadIdx.x >> 7;  // which 32 of the stage's 64 k-values
+    const int m = m0 + row;
+    const bool live = m < p.M;
+    int n = 0, ih0 = 0, iw0 = 0, pix = 0;
+    if (live) {
+      n = m / p.P;
+      pix = m - n * p.P;
+      const int oh = pix / p.OW, ow = pix - oh * p.OW;
+      ih0 = oh * p.SH - p.PHL;
+      iw0 = ow * p.SW - p.PWL;
+    }
+    const float *img = p.x + static_cast<int64_t>(n) * p.IC * p.H * p.W;
+    // pixels whose whole window lies inside the image skip the bounds tests
+    const bool interior = live && ih0 >= 0 && iw0 >= 0 && ih0 + (p.KH - 1) * p.DH < p.H &&
+                          iw0 + (p.KW - 1) * p.DW < p.W;
+    const int khw = p.KH * p.KW, hw = p.H * p.W;
+    const int pix_off = ih0 * p.W + iw0;
+    const uint32_t row_off = static_cast<uint32_t>(row) * 128u;
+    const uint32_t swz = static_cast<uint32_t>(row & 7);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    // loads of k-block kb into registers (no shared memory involved yet)
+    auto gather = [&](int kb, float (&v)[32]) __attribute__((always_inline)) {
+      const int k0 = kb * BK + half * 32;
+      if constexpr (TAP_MAJOR) {
+        const int q = k0 >> 5;  // this thread's group of 32 k-values = (channel block, tap)
+        const int icb = q / khw, tap = q - icb * khw;
+        const int ic0 = icb * 32;
+        const int kh = tap / p.KW, kw = tap - kh * p.KW;
+        const int ih = ih0 + kh * p.DH, iw = iw0 + kw * p.DW;
+        if (live && k0 < p.K && static_cast<unsigned>(ih) < static_cast<unsigned>(p.H) &&
+            static_cast<unsigned>(iw) < static_cast<unsigned>(p.W)) {
+          const float *src = img + ic0 * hw + ih * p.W + iw;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __ldg(src + j * hw);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+      } else if (k0 >= p.K || !live) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+      } else {
+        int ic = k0 / khw;
+        int r = k0 - ic * khw;
+        int kh = r / p.KW;
+        int kw = r - kh * p.KW;
+        // in batches of 16: offsets (pure integer work, no branches), then the loads, all in
+        // flight together; elements outside the image or beyond K read offset 0 of the image
+        // and are zeroed afterwards
+        uint32_t valid = 0;
+#pragma unroll
+        for (int b = 0; b < 32; b += 16) {
+          int off[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int dh = kh * p.DH, dw = kw * p.DW;
+            const bool inside = static_cast<unsigned>(ih0 + dh) < static_cast<unsigned>(p.H) &
+                                static_cast<unsigned>(iw0 + dw) < static_cast<unsigned>(p.W);
+            const bool in = (k0 + b + j < p.K) & (interior | inside);
+            off[j] = in ? ic * hw + dh * p.W + dw + pix_off : 0;
+            valid |= (in ? 1u : 0u) << (b + j);
+            const bool wrap_w = ++kw == p.KW;
+            kw = wrap_w ? 0 : kw;
+            kh += wrap_w ? 1 : 0;
+            const bool wrap_h = kh == p.KH;
+            kh = wrap_h ? 0 : kh;
+            ic += wrap_h ? 1 : 0;
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[b + j] = __ldg(img + off[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = (valid >> j) & 1u ? v[j] : 0.f;
+      }
+    };
+    // waits for the stage to be free, then converts and stores the row and hands it over
+    auto put = [&](float (&v)[32]) __attribute__((always_inline)) -> bool {
+      if (!mbar_wait_warp(&empty_bar[stage], phase ^ 1, abort_flag)) {
+        atomicCAS(p.err, 0u, 0x50000000u | static_cast<uint32_t>(stage));
+        return false;
+      }
+      uint8_t *sa = tiles + stage * stage_bytes;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const __half2 h0 = __floats2half2_rn(v[c * 8 + 0], v[c * 8 + 1]), h1 = __floats2half2_rn(v[c * 8 + 2], v[c * 8 + 3]);
+        const __half2 h2 = __floats2half2_rn(v[c * 8 + 4], v[c * 8 + 5]), h3 = __floats2half2_rn(v[c * 8 + 6], v[c * 8 + 7]);
+        uint4 q;
+        q.x = *reinterpret_cast<const uint32_t *>(&h0);
+        q.y = *reinterpret_cast<const uint32_t *>(&h1);
+        q.z = *reinterpret_cast<const uint32_t *>(&h2);
+        q.w = *reinterpret_cast<const uint32_t *>(&h3);
+        // 128-byte swizzle: 16-byte chunk c of row r lives at chunk (c ^ (r & 7))
+        const uint32_t chunk = static_cast<uint32_t>(half * 4 + c);
+        *reinterpret_cast<uint4 *>(sa + row_off + ((chunk ^ swz) << 4)) = q;
+      }
+      fence_proxy_async_smem();  // the tensor core reads these rows through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full_bar[stage]);
+      if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      return true;
+    };
+    for (int kb = 0; kb < p.num_kb; ++kb) {
+      float v[32];
+      gather(kb, v);
+      if (!put(v)) { ok = false; break; }
+    }
+
+    // ------- epilogue: thread = pixel, registers = channels; the two threads of a pixel -------
+    // ------- take alternate groups of 32 channels                                       -------
+    // (ok is uniform within a warp: the waits above are warp-wide)
+    if (ok && !mbar_wait_warp(&acc_bar, 0, abort_flag)) {
+      atomicCAS(p.err, 0u, 0x52000000u);
+      ok = false;
+    }
+    if (ok) {
+      tc_fence_after();
+      const int64_t out_base = static_cast<int64_t>(n) * p.OC * p.P + pix;
+      // a warp may only read the 32 tensor-memory lanes (warp % 4) * 32 ...
+      const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+      for (int c0 = half * 32; c0 < bn && n0 + c0 < p.OC; c0 += 64) {
+        uint32_t acc[32];
+        tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(c0), acc);
+        tmem_ld_wait_regs(acc);
+        if (live) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int oc = n0 + c0 + j;
+            if (oc < p.OC) {
+              const int64_t o = out_base + static_cast<int64_t>(oc) * p.P;
+              float v = __uint_as_float(acc[j]);
+              if (p.bias) v += __ldg(p.bias + oc);
+              if (p.add) v += __ldg(p.add + o);
+              if (p.relu) v = fmaxf(v, 0.f);
+              p.out[o] = v;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == GATHER_WARPS) {
+    // ------------------------- filter loader -------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t tx = static_cast<uint32_t>(bn * BK * 2);
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        if (!mbar_wait<40>(&empty_bar[stage], phase ^ 1, abort_flag)) {
+          atomicCAS(p.err, 0u, 0x51000000u | static_cast<uint32_t>(stage));
+          break;
+        }
+        mbar_arrive_expect_tx(&full_bar[stage], tx);
+        tma_load_2d(tiles + stage * stage_bytes + A_BYTES, &tmap_w, &full_bar[stage], kb * BK, n0);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------- MMA issuer -------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(BM, static_cast<uint32_t>(bn), false, false, false);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        if (!mbar_wait<20>(&full_bar[stage], phase, abort_flag)) {
+          atomicCAS(p.err, 0u, 0x53000000u | static_cast<uint32_t>(stage));
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(tiles + stage * stage_bytes);
+        const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
+        const uint64_t b_desc = make_smem_desc_sw128(sa + A_BYTES, 16, 1024);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)
+          umma_f16_ss(tmem_base, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k),
+                      idesc, (kb | k) != 0 ? 1u : 0u);
+        umma_commit(&empty_bar[stage]);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+      if (ok) umma_commit(&acc_bar);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == GATHER_WARPS) tmem_dealloc(tmem_base, static_cast<uint32_t>(bn));
+}
+
+
+// OIHW fp32 filter -> fp16 [OC][((ic / 32) * taps + tap) * 32 + ic % 32] (the k order of the
+// TAP_MAJOR kernel); IC is a multiple of 32
+__global__ void __launch_bounds__(256) pack_filter_tap_major(const float *__restrict__ w, __half *__restrict__ out,
+                                                             int OC, int IC, int taps) {
+  const int64_t total = static_cast<int64_t>(OC) * IC * taps;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int lane_ic = static_cast<int>(i & 31);
+    const int64_t t = i >> 5;
+    const int tap = static_cast<int>(t % taps);
+    const int64_t u = t / taps;
+    const int icb = static_cast<int>(u % (IC / 32));
+    const int64_t oc = u / (IC / 32);
+    out[i] = __float2half_rn(__ldg(w + (oc * IC + icb * 32 + lane_ic) * taps + tap));
+  }
+}
+
+}  // namespace mdc
+
+using namespace mdc;
+
+MDC_API void mgpuConv2d(float *input, float *weight, float *bias, float *output, float *postAdd, int64_t N,
+                        int64_t IC, int64_t H, int64_t W, int64_t OC, int64_t KH, int64_t KW, int64_t OH,
+                        int64_t OW, int64_t PHL, int64_t PWL, int64_t PHR, int64_t PWR, int64_t SH, int64_t SW,
+                        int64_t DH, int64_t DW, bool hasPostAdd, bool hasContainRelu, void *stream) {
+  if (N <= 0 || OC <= 0 || OH <= 0 || OW <= 0) return;
+  if (IC <= 0 || H <= 0 || W <= 0 || KH <= 0 || KW <= 0 || SH <= 0 || SW <= 0 || DH <= 0 || DW <= 0 ||
+      PHL < 0 || PWL < 0 || PHR < 0 || PWR < 0) {
+    fail("mgpuConv2d: sizes, strides and dilations must be positive, paddings non-negative");
+    return;
+  }
+  // the caller's output extent must be one its geometry can produce
+  if ((OH - 1) * SH + (KH - 1) * DH + 1 > H + PHL + PHR || (OW - 1) * SW + (KW - 1) * DW + 1 > W + PWL + PWR) {
+    fail("mgpuConv2d: output extent does not fit the padded input");
+    return;
+  }
+  if (hasPostAdd && !postAdd) { fail("mgpuConv2d: hasPostAdd without a postAdd tensor"); return; }
+  const int64_t M = N * OH * OW, K = IC * KH * KW;
+  // 32-bit index arithmetic inside the kernel
+  if (M > INT32_MAX - conv::BM || K > (1 << 24) || OC > (1 << 20) || IC * H * W > INT32_MAX ||
+      (H + PHL + PHR + KH * DH) * W > INT32_MAX) {
+    fail("mgpuConv2d: shape exceeds this library's index range");
+    return;
+  }
+  if (!device_info().ok) return;
+  cudaStream_t s = as_stream(stream);
+  const int64_t Kp = (K + 7) / 8 * 8;  // filter rows padded to 16-byte multiples for TMA
+  void *w16 = mgpuMemAllocAsync(static_cast<uint64_t>(OC) * Kp * 2, stream);
+  if (!w16) return;
+  const bool tap_major = IC % 32 == 0;
+  if (tap_major) {
+    const int64_t total = OC * K;
+    const int64_t blocks = (total + 255) / 256;
+    pack_filter_tap_major<<<static_cast<unsigned>(blocks < 4096 ? blocks : 4096), 256, 0, s>>>(
+        weight, static_cast<__half *>(w16), int(OC), int(IC), int(KH * KW));
+    check_cuda(cudaGetLastError(), "launch pack_filter_tap_major");
+    launched("mdc_pack_filter");
+  } else {
+    cast_rows_padded(weight, w16, OC, K, Kp, MGPU_DTYPE_F16, s);
+  }
+
+  conv::Params p;
+  p.x = input, p.bias = bias, p.add = hasPostAdd ? postAdd : nullptr, p.out = output;
+  p.IC = int(IC), p.H = int(H), p.W = int(W), p.OC = int(OC), p.KH = int(KH), p.KW = int(KW);
+  p.OH = int(OH), p.OW = int(OW), p.PHL = int(PHL), p.PWL = int(PWL), p.SH = int(SH), p.SW = int(SW);
+  p.DH = int(DH), p.DW = int(DW);
+  p.M = int(M), p.P = int(OH * OW), p.K = int(K), p.num_kb = int((K + conv::BK - 1) / conv::BK);
+  // channels per CTA: wide tiles gather each pixel's patch fewer times, but the grid should
+  // still cover the SMs
+  p.bn = OC <= 32 ? 32 : OC <= 64 ? 64 : OC <= 128 ? 128 : 256;
+  const int64_t m_tiles = (M + conv::BM - 1) / conv::BM;
+  while (p.bn > 64 && m_tiles * ((OC + p.bn - 1) / p.bn) < device_info().sms) p.bn /= 2;
+  p.relu = hasContainRelu ? 1 : 0;
+  p.err = device_error_slot();
+  CUtensorMap tw;
+  // rows beyond OC and k beyond Kp read as zero
+  if (p.err && encode_tmap_2d(&tw, w16, MGPU_DTYPE_F16, static_cast<uint64_t>(Kp), static_cast<uint64_t>(OC),
+                              static_cast<uint64_t>(Kp) * 2, conv::BK, static_cast<uint32_t>(p.bn))) {
+    const size_t smem = conv::smem_bytes(p.bn);
+    // dynamic shared memory limit for the largest tile, set once per device
+    static int attr_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+      const int limit = static_cast<int>(conv::smem_bytes(256));
+      if (check_cuda(cudaFuncSetAttribute(conv_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit),
+                     "cudaFuncSetAttribute(conv)") &&
+          check_cuda(cudaFuncSetAttribute(conv_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit),
+                     "cudaFuncSetAttribute(conv)"))
+        attr_dev = dev;
+    }
+    const dim3 grid(static_cast<unsigned>((M + conv::BM - 1) / conv::BM),
+                    static_cast<unsigned>((OC + p.bn - 1) / p.bn));
+    {
+      ProfileScope prof(kCatGemm, s);
+      if (tap_major) conv_tcgen05_kernel<true><<<grid, conv::THREADS, smem, s>>>(tw, p);
+      else conv_tcgen05_kernel<false><<<grid, conv::THREADS, smem, s>>>(tw, p);
+      check_cuda(cudaGetLastError(), "launch conv_tcgen05_kernel");
+    }
+    launched("conv_tcgen05_kernel");
+  }
+  mgpuMemFreeAsync(w16, stream);
+}

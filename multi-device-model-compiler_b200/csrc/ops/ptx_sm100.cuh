@@ -67,6 +67,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Waits for the phase with the given parity.  Returns false if `*abort_flag` (shared
 // memory, set by any role that gave up) becomes non-zero or the time limit passes; the
 // caller then records an error and leaves its loop.
+// SLEEP_NS > 0 puts the thread to sleep between polls: for kernels in which many warps wait
+// at once, whose polling would otherwise take the issue slots of the warps doing the work.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
                                           volatile uint32_t *abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -74,6 +77,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+    if constexpr (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
     if ((++spins & 0x3f) == 0) {
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
@@ -82,6 +86,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
       }
     }
   }
+}
+
+// The same wait for a whole (converged) warp: lane 0 polls, the others are released by the
+// shuffle.  Keeps 31 of 32 threads off the barrier word and off the global timer, which is
+// slow to read when hundreds of threads do so at once.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity,
+                                               volatile uint32_t *abort_flag) {
+  uint32_t ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait<40>(bar, parity, abort_flag) ? 1u : 0u;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
 }
 
 // ---------------- TMA (cp.async.bulk.tensor), plain tile copies only ----------------
