@@ -159,6 +159,16 @@ void mgpuEncoderStackDestroy(void *stack);
 void mgpuEncoderStackRunHost(void *stack, const float *x_host, const int32_t *seq_lens_host,
                              float *y_host, int64_t batch, int64_t seq_len, int32_t chunks);
 
+/* Pipelined form for a stream of batches (no counterpart in the reference).  Submit queues
+ * upload, stack and download of one whole batch on three streams and returns a ticket at once;
+ * consecutive submissions alternate between two sets of device IO buffers, so batch i+1 uploads
+ * while batch i computes and batch i-1 downloads.  x_host / seq_lens_host must stay unchanged
+ * and y_host untouched until WaitHost(ticket) returns; at most two submissions may be waiting
+ * (a third Submit simply queues behind the first's download).  Returns -1 on failure. */
+int64_t mgpuEncoderStackSubmitHost(void *stack, const float *x_host, const int32_t *seq_lens_host,
+                                   float *y_host, int64_t batch, int64_t seq_len);
+void mgpuEncoderStackWaitHost(void *stack, int64_t ticket);
+
 /* One post-/pre-LN encoder layer in a single call: the argument list of
  * mgpuLLMDecodingContextLayer extended by what the encoder configs need. */
 void mgpuTransformerEncoderLayer(const float *input, const float *qkv_weight, const float *qkv_bias,

@@ -109,6 +109,8 @@ OPS_SIGNATURES = {
     "mgpuEncoderStackRun": (None, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     "mgpuEncoderStackDestroy": (None, [_vp]),
     "mgpuEncoderStackRunHost": (None, [_vp, _vp, _vp, _vp, _i64, _i64, _i32]),
+    "mgpuEncoderStackSubmitHost": (_i64, [_vp, _vp, _vp, _vp, _i64, _i64]),
+    "mgpuEncoderStackWaitHost": (None, [_vp, _i64]),
     "mgpuTransformerEncoderLayer": (None, [_vp] * 15 + [_i64] * 5 + [_b, _b, _i32, _i32, _f, _vp]),
     "mgpuOpsLaunchCount": (_u64, []),
     "mgpuOpsCheckDeviceStatus": (_u32, [_vp]),
@@ -455,6 +457,23 @@ class EncoderStack:
         lens = np.ascontiguousarray(seq_lens, dtype=np.int32) if seq_lens is not None else None
         ops().mgpuEncoderStackRunHost(self.h, x.ctypes.data, lens.ctypes.data if lens is not None else None,
                                       y.ctypes.data, B, S, chunks)
+
+    def submit_host(self, x: np.ndarray, y: np.ndarray, seq_lens=None) -> int:
+        """Queue one batch (upload, stack, download) and return its ticket without waiting.  x, y
+        (and seq_lens, int32) must stay alive and untouched until wait_host(ticket)."""
+        B, S, _ = x.shape
+        if seq_lens is not None and (seq_lens.dtype != np.int32 or not seq_lens.flags.c_contiguous):
+            raise ValueError("seq_lens must be a C-contiguous int32 array that outlives the call")
+        t = ops().mgpuEncoderStackSubmitHost(self.h, x.ctypes.data, seq_lens.ctypes.data if seq_lens is not None else None,
+                                             y.ctypes.data, B, S)
+        if t < 0:
+            check("mgpuEncoderStackSubmitHost")
+            raise MdcError("mgpuEncoderStackSubmitHost failed")
+        return t
+
+    def wait_host(self, ticket: int) -> None:
+        ops().mgpuEncoderStackWaitHost(self.h, ticket)
+        check("mgpuEncoderStackWaitHost")
 
     def close(self):
         if self.h:

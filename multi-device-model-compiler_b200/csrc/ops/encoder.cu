@@ -42,7 +42,9 @@ struct EncoderStack {
   cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_comp[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
   void *x_dev[2] = {nullptr, nullptr}, *y_dev[2] = {nullptr, nullptr};
   int32_t *lens_dev[2] = {nullptr, nullptr};
-  int64_t pipe_seqs = 0, pipe_seq_len = 0;
+  int64_t pipe_tokens = 0, pipe_seqs = 0;  // capacity of the IO buffers (tokens) and of the lengths buffers
+  bool slot_used[2] = {false, false};  // the slot's events have been recorded at least once
+  int64_t tickets = 0;                 // submissions made through mgpuEncoderStackSubmitHost
   // recorded at the end of every run; the next run (on any stream) waits for it, because
   // all runs of a stack share one activation workspace
   cudaEvent_t done_ev = nullptr;
@@ -247,6 +249,70 @@ MDC_API void mgpuEncoderStackDestroy(void *stack) {
   destroy_stack(st, nullptr);
 }
 
+// Streams, events and the two sets of device IO buffers of the host-buffer pipeline, sized
+// for `per` sequences.  Growing the buffers first drains whatever is still in flight.
+static bool ensure_pipe(EncoderStack *st, int64_t per, int64_t seq_len) {
+  const int64_t d = st->d;
+  if (!st->s_in) {
+    bool ok = check_cuda(cudaStreamCreateWithFlags(&st->s_in, cudaStreamNonBlocking), "stream") &&
+              check_cuda(cudaStreamCreateWithFlags(&st->s_comp, cudaStreamNonBlocking), "stream") &&
+              check_cuda(cudaStreamCreateWithFlags(&st->s_out, cudaStreamNonBlocking), "stream");
+    for (int i = 0; ok && i < 2; ++i)
+      ok = check_cuda(cudaEventCreateWithFlags(&st->ev_in[i], cudaEventDisableTiming), "event") &&
+           check_cuda(cudaEventCreateWithFlags(&st->ev_comp[i], cudaEventDisableTiming), "event") &&
+           check_cuda(cudaEventCreateWithFlags(&st->ev_out[i], cudaEventDisableTiming), "event");
+    if (!ok) return false;
+  }
+  if (st->pipe_tokens < per * seq_len || st->pipe_seqs < per) {
+    cudaStreamSynchronize(st->s_in);
+    cudaStreamSynchronize(st->s_comp);
+    cudaStreamSynchronize(st->s_out);
+    const int64_t tokens = st->pipe_tokens > per * seq_len ? st->pipe_tokens : per * seq_len;
+    const int64_t seqs = st->pipe_seqs > per ? st->pipe_seqs : per;
+    for (int i = 0; i < 2; ++i) {
+      if (st->x_dev[i]) mgpuMemFreeAsync(st->x_dev[i], st->s_comp);
+      if (st->y_dev[i]) mgpuMemFreeAsync(st->y_dev[i], st->s_comp);
+      if (st->lens_dev[i]) mgpuMemFreeAsync(st->lens_dev[i], st->s_comp);
+      const uint64_t bytes = static_cast<uint64_t>(tokens) * d * 4;
+      st->x_dev[i] = mgpuMemAllocAsync(bytes, st->s_comp);
+      st->y_dev[i] = mgpuMemAllocAsync(bytes, st->s_comp);
+      st->lens_dev[i] = static_cast<int32_t *>(mgpuMemAllocAsync(static_cast<uint64_t>(seqs) * 4, st->s_comp));
+      if (!st->x_dev[i] || !st->y_dev[i] || !st->lens_dev[i]) {
+        st->pipe_tokens = st->pipe_seqs = 0;
+        fail("encoder stack: out of device memory for the IO buffers");
+        return false;
+      }
+    }
+    st->pipe_tokens = tokens;
+    st->pipe_seqs = seqs;
+    check_cuda(cudaStreamSynchronize(st->s_comp), "sync");
+  }
+  order_after_previous(st, st->s_comp);
+  return ensure_ws(st, per * seq_len, st->s_comp);
+}
+
+// upload -> stack -> download of nb sequences through IO buffer set `set`, each stage on its
+// own stream, ordered against the previous user of the same set by events
+static void enqueue_host_chunk(EncoderStack *st, int set, const float *x_host, const int32_t *lens_host,
+                               float *y_host, int64_t nb, int64_t seq_len) {
+  const size_t elems = static_cast<size_t>(nb) * seq_len * st->d;
+  if (st->slot_used[set]) cudaStreamWaitEvent(st->s_in, st->ev_comp[set], 0);  // x_dev[set] consumed
+  check_cuda(cudaMemcpyAsync(st->x_dev[set], x_host, elems * 4, cudaMemcpyHostToDevice, st->s_in), "H2D");
+  if (lens_host)
+    check_cuda(cudaMemcpyAsync(st->lens_dev[set], lens_host, nb * 4, cudaMemcpyHostToDevice, st->s_in), "H2D lens");
+  cudaEventRecord(st->ev_in[set], st->s_in);
+  cudaStreamWaitEvent(st->s_comp, st->ev_in[set], 0);
+  if (st->slot_used[set]) cudaStreamWaitEvent(st->s_comp, st->ev_out[set], 0);  // y_dev[set] drained
+  run_stack(st, static_cast<const float *>(st->x_dev[set]), lens_host ? st->lens_dev[set] : nullptr,
+            static_cast<float *>(st->y_dev[set]), nb, seq_len, st->s_comp);
+  cudaEventRecord(st->ev_comp[set], st->s_comp);
+  mark_run_done(st, st->s_comp);
+  cudaStreamWaitEvent(st->s_out, st->ev_comp[set], 0);
+  check_cuda(cudaMemcpyAsync(y_host, st->y_dev[set], elems * 4, cudaMemcpyDeviceToHost, st->s_out), "D2H");
+  cudaEventRecord(st->ev_out[set], st->s_out);
+  st->slot_used[set] = true;
+}
+
 MDC_API void mgpuEncoderStackRunHost(void *stack, const float *x_host, const int32_t *seq_lens_host,
                                      float *y_host, int64_t batch, int64_t seq_len, int32_t chunks) {
   EncoderStack *st = static_cast<EncoderStack *>(stack);
@@ -270,60 +336,41 @@ MDC_API void mgpuEncoderStackRunHost(void *stack, const float *x_host, const int
   }
   int64_t per = 0;  // largest chunk: sizes the device buffers and the workspace
   for (int64_t v : sizes) per = v > per ? v : per;
+  if (!ensure_pipe(st, per, seq_len)) return;
   const int64_t d = st->d;
-  if (!st->s_in) {
-    bool ok = check_cuda(cudaStreamCreateWithFlags(&st->s_in, cudaStreamNonBlocking), "stream") &&
-              check_cuda(cudaStreamCreateWithFlags(&st->s_comp, cudaStreamNonBlocking), "stream") &&
-              check_cuda(cudaStreamCreateWithFlags(&st->s_out, cudaStreamNonBlocking), "stream");
-    for (int i = 0; ok && i < 2; ++i)
-      ok = check_cuda(cudaEventCreateWithFlags(&st->ev_in[i], cudaEventDisableTiming), "event") &&
-           check_cuda(cudaEventCreateWithFlags(&st->ev_comp[i], cudaEventDisableTiming), "event") &&
-           check_cuda(cudaEventCreateWithFlags(&st->ev_out[i], cudaEventDisableTiming), "event");
-    if (!ok) return;
-  }
-  if (st->pipe_seqs < per || st->pipe_seq_len < seq_len) {
-    for (int i = 0; i < 2; ++i) {
-      if (st->x_dev[i]) mgpuMemFreeAsync(st->x_dev[i], st->s_comp);
-      if (st->y_dev[i]) mgpuMemFreeAsync(st->y_dev[i], st->s_comp);
-      if (st->lens_dev[i]) mgpuMemFreeAsync(st->lens_dev[i], st->s_comp);
-      const uint64_t bytes = static_cast<uint64_t>(per) * seq_len * d * 4;
-      st->x_dev[i] = mgpuMemAllocAsync(bytes, st->s_comp);
-      st->y_dev[i] = mgpuMemAllocAsync(bytes, st->s_comp);
-      st->lens_dev[i] = static_cast<int32_t *>(mgpuMemAllocAsync(static_cast<uint64_t>(per) * 4, st->s_comp));
-      if (!st->x_dev[i] || !st->y_dev[i] || !st->lens_dev[i]) { fail("encoder stack: out of device memory for the IO buffers"); return; }
-    }
-    st->pipe_seqs = per;
-    st->pipe_seq_len = seq_len;
-    check_cuda(cudaStreamSynchronize(st->s_comp), "sync");
-  }
-  order_after_previous(st, st->s_comp);
-  if (!ensure_ws(st, per * seq_len, st->s_comp)) return;
   int n = 0;
   int64_t b0 = 0;
   for (size_t ci = 0; ci < sizes.size(); b0 += sizes[ci], ++ci, ++n) {
-    const int set = n & 1;
     const int64_t nb = sizes[ci];
     if (nb <= 0) continue;
-    const size_t elems = static_cast<size_t>(nb) * seq_len * d;
     const size_t off = static_cast<size_t>(b0) * seq_len * d;
-    if (n >= 2) cudaStreamWaitEvent(st->s_in, st->ev_comp[set], 0);  // x_dev[set] consumed
-    check_cuda(cudaMemcpyAsync(st->x_dev[set], x_host + off, elems * 4, cudaMemcpyHostToDevice, st->s_in), "H2D");
-    if (seq_lens_host)
-      check_cuda(cudaMemcpyAsync(st->lens_dev[set], seq_lens_host + b0, nb * 4, cudaMemcpyHostToDevice, st->s_in), "H2D lens");
-    cudaEventRecord(st->ev_in[set], st->s_in);
-    cudaStreamWaitEvent(st->s_comp, st->ev_in[set], 0);
-    if (n >= 2) cudaStreamWaitEvent(st->s_comp, st->ev_out[set], 0);  // y_dev[set] drained
-    run_stack(st, static_cast<const float *>(st->x_dev[set]), seq_lens_host ? st->lens_dev[set] : nullptr,
-              static_cast<float *>(st->y_dev[set]), nb, seq_len, st->s_comp);
-    cudaEventRecord(st->ev_comp[set], st->s_comp);
-    mark_run_done(st, st->s_comp);
-    cudaStreamWaitEvent(st->s_out, st->ev_comp[set], 0);
-    check_cuda(cudaMemcpyAsync(y_host + off, st->y_dev[set], elems * 4, cudaMemcpyDeviceToHost, st->s_out), "D2H");
-    cudaEventRecord(st->ev_out[set], st->s_out);
+    enqueue_host_chunk(st, n & 1, x_host + off, seq_lens_host ? seq_lens_host + b0 : nullptr, y_host + off, nb, seq_len);
   }
   check_cuda(cudaStreamSynchronize(st->s_out), "sync");
   check_cuda(cudaStreamSynchronize(st->s_comp), "sync");
   check_cuda(cudaStreamSynchronize(st->s_in), "sync");
+}
+
+// Pipelined form of RunHost for a stream of batches: Submit queues upload, stack and download
+// of one whole batch and returns at once; consecutive submissions alternate between the two
+// IO buffer sets, so batch i+1 is uploaded while batch i computes and batch i-1 downloads.
+MDC_API int64_t mgpuEncoderStackSubmitHost(void *stack, const float *x_host, const int32_t *seq_lens_host,
+                                           float *y_host, int64_t batch, int64_t seq_len) {
+  EncoderStack *st = static_cast<EncoderStack *>(stack);
+  if (!st) { fail("mgpuEncoderStackSubmitHost: null handle"); return -1; }
+  if (batch <= 0 || seq_len <= 0 || !x_host || !y_host) { fail("mgpuEncoderStackSubmitHost: empty batch or null buffer"); return -1; }
+  if (!ensure_pipe(st, batch, seq_len)) return -1;
+  enqueue_host_chunk(st, static_cast<int>(st->tickets & 1), x_host, seq_lens_host, y_host, batch, seq_len);
+  return st->tickets++;
+}
+
+MDC_API void mgpuEncoderStackWaitHost(void *stack, int64_t ticket) {
+  EncoderStack *st = static_cast<EncoderStack *>(stack);
+  if (!st) { fail("mgpuEncoderStackWaitHost: null handle"); return; }
+  if (ticket < 0 || ticket >= st->tickets) { fail("mgpuEncoderStackWaitHost: unknown ticket"); return; }
+  // downloads complete in submission order on one stream: the latest event recorded on the
+  // ticket's buffer set is at or after the ticket's own
+  check_cuda(cudaEventSynchronize(st->ev_out[ticket & 1]), "wait for the download");
 }
 
 MDC_API void mgpuTransformerEncoderLayer(const float *input, const float *qkv_weight, const float *qkv_bias,

@@ -135,6 +135,41 @@ def test_stack_and_batch_independence(m):
     st.close()
 
 
+def test_pipelined_submissions_match_single_runs(m):
+    """Five batches of different sizes (with and without lengths) submitted back to back through
+    SubmitHost / WaitHost: every result equals the device-pointer run of the same batch, bit for
+    bit, whatever was in flight around it."""
+    rng = np.random.default_rng(8)
+    L, S, d, F, H = 2, 64, 256, 512, 4
+    layers = [make_layer(rng, d, F) for _ in range(L)]
+    st = m.EncoderStack(layers, H)
+    batches = []
+    for B, with_lens in ((6, False), (16, True), (3, True), (16, False), (9, True)):
+        x = rng.standard_normal((B, S, d)).astype(np.float32)
+        lens = rng.integers(1, S + 1, B).astype(np.int32) if with_lens else None
+        batches.append((x, lens, np.full_like(x, np.nan)))
+    expect = [st.run(x, lens) for x, lens, _ in batches]
+    tickets = []
+    for i, (x, lens, y) in enumerate(batches):
+        tickets.append(st.submit_host(x, y, lens))
+        if i >= 1:
+            st.wait_host(tickets[i - 1])  # one batch behind: two are in flight at a time
+            assert np.array_equal(batches[i - 1][2], expect[i - 1], equal_nan=True)
+    st.wait_host(tickets[-1])
+    assert np.array_equal(batches[-1][2], expect[-1], equal_nan=True)
+    assert tickets == list(range(len(batches)))
+    assert m.ops().mgpuOpsCheckDeviceStatus(None) == 0
+    # waiting again, or for an older ticket, returns at once; an unknown ticket is an error
+    st.wait_host(tickets[0])
+    with pytest.raises(m.MdcError):
+        st.wait_host(99)
+    # the synchronous host call still works after pipelined use
+    y = np.empty_like(batches[1][0])
+    st.run_host(batches[1][0], y, batches[1][1], chunks=3)
+    assert np.array_equal(y, expect[1], equal_nan=True)
+    st.close()
+
+
 def test_reference_decoder_fixture(m, golden):
     # benchmark/PyTorch/Models/LLM.py (pre-LN, causal, ReLU) computed in fp32 by the reference's
     # model definition; the GPU layer runs it with fp16 storage
