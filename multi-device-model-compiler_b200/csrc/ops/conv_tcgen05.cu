@@ -47,27 +47,39 @@ constexpr int THREADS = (GATHER_WARPS + 2) * 32;  // + filter loader, MMA issuer
 struct Params {
   const float *x, *bias, *add;
   float *out;
-  int IC, H, W, OC, KH, KW, OH, OW, PHL, PWL, SH, SW, DH, DW;
+  int IC, H, W, OC, KH, KW, OH, OW, PHL, PWL, PHR, PWR, SH, SW, DH, DW;
+  int tile_bytes;       // MODE 2: size of one staged input tile (two are kept)
   int M, P, K, num_kb;  // pixels in total, pixels per image, IC*KH*KW, k-blocks
   int bn;               // channels per CTA: 32, 64, 128 or 256
   int relu;
   uint32_t *err;
 };
 
-inline size_t smem_bytes(int bn) { return size_t(STAGES) * (A_BYTES + bn * BK * 2) + 1024; }
+inline size_t smem_bytes(int bn, int tile_bytes = 0) {
+  return size_t(STAGES) * (A_BYTES + bn * BK * 2) + 2 * size_t(tile_bytes) + 1024;
+}
+constexpr size_t kMaxSmem = 226 * 1024;  // dynamic part; the static part (barriers) stays under the remaining 1 KiB
 }  // namespace conv
 
-// TAP_MAJOR (IC a multiple of 32): k = ((ic / 32) * KH*KW + kh*KW + kw) * 32 + ic % 32, so the
+// Tap-major order (IC a multiple of 32): k = ((ic / 32) * KH*KW + kh*KW + kw) * 32 + ic % 32, so the
 // 32 k-values a gather thread handles share one filter tap (one bounds test, 32 loads a
 // channel plane apart) and consecutive k-blocks walk the taps of the same 32 channels, whose
 // input lines are then re-served by L1 instead of L2.
 // Otherwise k = (ic*KH + kh)*KW + kw (the filter's own order) and every element carries its
 // own tap arithmetic.
-template <bool TAP_MAJOR>
-__global__ void __launch_bounds__(conv::THREADS, 3)
+//
+// MODE 0: the filter's own k order, gathered element by element from global memory.
+// MODE 1: the k order above, each thread's 32 values loaded from global memory.
+// MODE 2: the k order above; the gather warps first stage the input rows the CTA's pixels touch
+//         (32 channels at a time, zero padding included, [row][column][channel] in 16 bits) in
+//         shared memory with coalesced loads, and every tap of those channels is then a
+//         64-byte shared-memory copy per thread, without bounds tests.
+template <int MODE>
+__global__ void __launch_bounds__(conv::THREADS, MODE == 2 ? 2 : 3)
 conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const conv::Params p) {
   using namespace conv;
   using namespace ptx;
+  constexpr bool TAP_MAJOR = MODE != 0;
   extern __shared__ uint8_t smem_dyn[];
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
   __shared__ uint32_t tmem_slot, abort_flag_s;
@@ -205,10 +217,100 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const conv::Para
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
       return true;
     };
-    for (int kb = 0; kb < p.num_kb; ++kb) {
-      float v[32];
-      gather(kb, v);
-      if (!put(v)) { ok = false; break; }
+    if constexpr (MODE == 2) {
+      // Rows of the padded input are numbered g = image * Hp + padded row; the CTA's pixels touch
+      // the rows [g_base, g_base + span) (the padding rows between two images included).
+      const int Hp = p.H + p.PHL + p.PHR, Wp = p.W + p.PWL + p.PWR;
+      const int ml = min(m0 + BM - 1, p.M - 1);
+      const int nf = m0 / p.P, ohf = (m0 - nf * p.P) / p.OW;
+      const int nl = ml / p.P, ohl = (ml - nl * p.P) / p.OW;
+      const int g_base = nf * Hp + ohf * p.SH;
+      const int span = nl * Hp + ohl * p.SH + (p.KH - 1) * p.DH - g_base + 1;
+      uint8_t *T = tiles + STAGES * stage_bytes;
+      // this thread's pixel, clamped to the last real one so that every read stays in the tile
+      const int mc = min(m, p.M - 1);
+      const int nc = mc / p.P, pc = mc - nc * p.P, ohc = pc / p.OW, owc = pc - ohc * p.OW;
+      const int g_pix = nc * Hp + ohc * p.SH - g_base, iw_pix = owc * p.SW;
+      const int ngroups = p.K >> 5;
+      int staged_upto = -1;
+      // one thread per position (row, column) and all 32 channels: neighbouring lanes hold
+      // neighbouring columns, so each of the 32 loads is a coalesced line and all of them are in
+      // flight together; the values leave as four 16-byte stores
+      auto stage_tile = [&](int icb) {
+        uint8_t *Tb = T + (icb & 1) * p.tile_bytes;
+        const int positions = span * Wp;
+        for (int pos = threadIdx.x; pos < positions; pos += GATHER_WARPS * 32) {
+          const int g = pos / Wp, iwp = pos - g * Wp;
+          const int G = g + g_base, nn = G / Hp, ih = G - nn * Hp - p.PHL, iw = iwp - p.PWL;
+          float e[32];
+          if (static_cast<unsigned>(ih) < static_cast<unsigned>(p.H) && static_cast<unsigned>(iw) < static_cast<unsigned>(p.W)) {
+            const float *src = p.x + (static_cast<int64_t>(nn) * p.IC + icb * 32) * hw + ih * p.W + iw;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) e[j] = __ldg(src + j * hw);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) e[j] = 0.f;
+          }
+          uint8_t *dst = Tb + pos * 64;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const __half2 h0 = __floats2half2_rn(e[c * 8 + 0], e[c * 8 + 1]), h1 = __floats2half2_rn(e[c * 8 + 2], e[c * 8 + 3]);
+            const __half2 h2 = __floats2half2_rn(e[c * 8 + 4], e[c * 8 + 5]), h3 = __floats2half2_rn(e[c * 8 + 6], e[c * 8 + 7]);
+            uint4 q;
+            q.x = *reinterpret_cast<const uint32_t *>(&h0);
+            q.y = *reinterpret_cast<const uint32_t *>(&h1);
+            q.z = *reinterpret_cast<const uint32_t *>(&h2);
+            q.w = *reinterpret_cast<const uint32_t *>(&h3);
+            // the four 16-byte pieces of a position are XOR-ed with its column, which spreads a
+            // warp's accesses over the banks
+            *reinterpret_cast<uint4 *>(dst + ((c ^ (iwp & 3)) << 4)) = q;
+          }
+        }
+      };
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        // every gather warp passes the same barriers whatever happened to its waits, so a
+        // warp that gave up cannot strand the others
+        const int need = min(2 * kb + 1, ngroups - 1) / khw;
+        while (staged_upto < need) {
+          asm volatile("bar.sync 1, %0;" ::"n"(GATHER_WARPS * 32) : "memory");  // the buffer's last readers are done
+          if (ok) stage_tile(staged_upto + 1);
+          ++staged_upto;
+          asm volatile("bar.sync 1, %0;" ::"n"(GATHER_WARPS * 32) : "memory");
+        }
+        if (!ok) continue;
+        if (!mbar_wait_warp(&empty_bar[stage], phase ^ 1, abort_flag)) {
+          atomicCAS(p.err, 0u, 0x50000000u | static_cast<uint32_t>(stage));
+          ok = false;
+          continue;
+        }
+        uint8_t *sa = tiles + stage * stage_bytes;
+        const int q = 2 * kb + half;
+        uint4 piece[4];
+        if (q < ngroups) {
+          const int icb = q / khw, tap = q - icb * khw;
+          const int kh = tap / p.KW, kw = tap - kh * p.KW;
+          const int iwp = iw_pix + kw * p.DW;
+          const uint8_t *src = T + (icb & 1) * p.tile_bytes + ((g_pix + kh * p.DH) * Wp + iwp) * 64;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) piece[c] = *reinterpret_cast<const uint4 *>(src + ((c ^ (iwp & 3)) << 4));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) piece[c] = make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          *reinterpret_cast<uint4 *>(sa + row_off + ((static_cast<uint32_t>(half * 4 + c) ^ swz) << 4)) = piece[c];
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_bar[stage]);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    } else {
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        float v[32];
+        gather(kb, v);
+        if (!put(v)) { ok = false; break; }
+      }
     }
 
     // ------- epilogue: thread = pixel, registers = channels; the two threads of a pixel -------
@@ -223,21 +325,33 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const conv::Para
       const int64_t out_base = static_cast<int64_t>(n) * p.OC * p.P + pix;
       // a warp may only read the 32 tensor-memory lanes (warp % 4) * 32 ...
       const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-      for (int c0 = half * 32; c0 < bn && n0 + c0 < p.OC; c0 += 64) {
-        uint32_t acc[32];
-        tmem_ld_32x32(tmem_base + lane_base + static_cast<uint32_t>(c0), acc);
-        tmem_ld_wait_regs(acc);
-        if (live) {
+      // 16 channels at a time: bias and postAdd values are fetched as one batch of independent
+      // loads while the accumulator load is in flight, never one load between two stores
+      for (int c32 = half * 32; c32 < bn && n0 + c32 < p.OC; c32 += 64) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int oc = n0 + c0 + j;
-            if (oc < p.OC) {
-              const int64_t o = out_base + static_cast<int64_t>(oc) * p.P;
-              float v = __uint_as_float(acc[j]);
-              if (p.bias) v += __ldg(p.bias + oc);
-              if (p.add) v += __ldg(p.add + o);
-              if (p.relu) v = fmaxf(v, 0.f);
-              p.out[o] = v;
+        for (int c0 = c32; c0 < c32 + 32; c0 += 16) {
+          const int oc0 = n0 + c0;
+          if (oc0 >= p.OC) break;  // uniform across the warp
+          uint32_t acc[16];
+          tmem_ld_32x16(tmem_base + lane_base + static_cast<uint32_t>(c0), acc);
+          float extra[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) extra[j] = (p.bias && oc0 + j < p.OC) ? __ldg(p.bias + oc0 + j) : 0.f;
+          if (p.add && live) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (oc0 + j < p.OC) extra[j] += __ldg(p.add + out_base + static_cast<int64_t>(oc0 + j) * p.P);
+          }
+          tmem_ld_wait_regs(acc);
+          if (live) {
+            float *dst = p.out + out_base + static_cast<int64_t>(oc0) * p.P;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (oc0 + j < p.OC) {
+                float v = __uint_as_float(acc[j]) + extra[j];
+                if (p.relu) v = fmaxf(v, 0.f);
+                dst[static_cast<int64_t>(j) * p.P] = v;
+              }
             }
           }
         }
@@ -358,7 +472,7 @@ MDC_API void mgpuConv2d(float *input, float *weight, float *bias, float *output,
   p.x = input, p.bias = bias, p.add = hasPostAdd ? postAdd : nullptr, p.out = output;
   p.IC = int(IC), p.H = int(H), p.W = int(W), p.OC = int(OC), p.KH = int(KH), p.KW = int(KW);
   p.OH = int(OH), p.OW = int(OW), p.PHL = int(PHL), p.PWL = int(PWL), p.SH = int(SH), p.SW = int(SW);
-  p.DH = int(DH), p.DW = int(DW);
+  p.DH = int(DH), p.DW = int(DW), p.PHR = int(PHR), p.PWR = int(PWR), p.tile_bytes = 0;
   p.M = int(M), p.P = int(OH * OW), p.K = int(K), p.num_kb = int((K + conv::BK - 1) / conv::BK);
   // channels per CTA: wide tiles gather each pixel's patch fewer times, but the grid should
   // still cover the SMs
@@ -371,16 +485,37 @@ MDC_API void mgpuConv2d(float *input, float *weight, float *bias, float *output,
   // rows beyond OC and k beyond Kp read as zero
   if (p.err && encode_tmap_2d(&tw, w16, MGPU_DTYPE_F16, static_cast<uint64_t>(Kp), static_cast<uint64_t>(OC),
                               static_cast<uint64_t>(Kp) * 2, conv::BK, static_cast<uint32_t>(p.bn))) {
-    const size_t smem = conv::smem_bytes(p.bn);
-    // dynamic shared memory limit for the largest tile, set once per device
+    // Staged mode: an upper bound of the padded input rows one CTA's 128 pixels touch.  The
+    // pixels cross at most `turns` row boundaries, each a step of SH rows or, between two
+    // images, of the rows left over at the bottom of one image and the top of the next.
+    int mode = tap_major ? 1 : 0;
+    if (tap_major && getenv("MDC_CONV_DIRECT") == nullptr) {
+      const int64_t Hp = H + PHL + PHR, Wp = W + PWL + PWR;
+      const int64_t turns = (conv::BM - 2 + OW) / OW;
+      const int64_t crossings = turns < (turns + OH - 1) / OH ? turns : (turns + OH - 1) / OH;
+      const int64_t cross_step = Hp - (OH - 1) * SH > SH ? Hp - (OH - 1) * SH : SH;
+      const int64_t span = (turns - crossings) * SH + crossings * cross_step + (KH - 1) * DH + 1;
+      const int64_t tile_bytes = span * Wp * 64;
+      // only when two CTAs still fit on an SM: alone, a CTA cannot hide its staging loads
+      // (measured: 32x64x56x56 -> 64 takes 90 us staged with one CTA per SM, 53 us direct;
+      // 32x256x14x14 -> 256 takes 61 us staged with two CTAs per SM, 66 us direct)
+      if (2 * (conv::smem_bytes(p.bn, static_cast<int>(tile_bytes < (1 << 20) ? tile_bytes : (1 << 20))) + 1024) <= conv::kMaxSmem) {
+        mode = 2;
+        p.tile_bytes = static_cast<int>(tile_bytes);
+      }
+    }
+    const size_t smem = conv::smem_bytes(p.bn, p.tile_bytes);
+    // dynamic shared memory limit, raised once per device
     static int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_dev != dev) {
-      const int limit = static_cast<int>(conv::smem_bytes(256));
-      if (check_cuda(cudaFuncSetAttribute(conv_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit),
+      const int limit = static_cast<int>(conv::kMaxSmem);
+      if (check_cuda(cudaFuncSetAttribute(conv_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit),
                      "cudaFuncSetAttribute(conv)") &&
-          check_cuda(cudaFuncSetAttribute(conv_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit),
+          check_cuda(cudaFuncSetAttribute(conv_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit),
+                     "cudaFuncSetAttribute(conv)") &&
+          check_cuda(cudaFuncSetAttribute(conv_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, limit),
                      "cudaFuncSetAttribute(conv)"))
         attr_dev = dev;
     }
@@ -388,8 +523,9 @@ MDC_API void mgpuConv2d(float *input, float *weight, float *bias, float *output,
                     static_cast<unsigned>((OC + p.bn - 1) / p.bn));
     {
       ProfileScope prof(kCatGemm, s);
-      if (tap_major) conv_tcgen05_kernel<true><<<grid, conv::THREADS, smem, s>>>(tw, p);
-      else conv_tcgen05_kernel<false><<<grid, conv::THREADS, smem, s>>>(tw, p);
+      if (mode == 2) conv_tcgen05_kernel<2><<<grid, conv::THREADS, smem, s>>>(tw, p);
+      else if (mode == 1) conv_tcgen05_kernel<1><<<grid, conv::THREADS, smem, s>>>(tw, p);
+      else conv_tcgen05_kernel<0><<<grid, conv::THREADS, smem, s>>>(tw, p);
       check_cuda(cudaGetLastError(), "launch conv_tcgen05_kernel");
     }
     launched("conv_tcgen05_kernel");

@@ -72,15 +72,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
                                           volatile uint32_t *abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
+  // The global timer is slow to read, so the clock of the time limit only starts at the
+  // 64th failed poll: an ordinary wait never touches it.
+  unsigned long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if constexpr (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
     if ((++spins & 0x3f) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitTimeoutNs) {
         *abort_flag = 1;
         return false;
       }
@@ -197,6 +201,14 @@ __device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&r)[32]) {
                  "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]),
                  "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]),
                  "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                 "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]),
+                 "+r"(r[14]), "+r"(r[15])
                :
                : "memory");
 }
