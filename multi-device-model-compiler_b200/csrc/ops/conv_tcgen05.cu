@@ -364,7 +364,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const conv::Para
       uint32_t phase = 0;
       const uint32_t tx = static_cast<uint32_t>(bn * BK * 2);
       for (int kb = 0; kb < p.num_kb; ++kb) {
-        if (!mbar_wait<40>(&empty_bar[stage], phase ^ 1, abort_flag)) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
           atomicCAS(p.err, 0u, 0x51000000u | static_cast<uint32_t>(stage));
           break;
         }
@@ -381,7 +381,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const conv::Para
       uint32_t phase = 0;
       bool ok = true;
       for (int kb = 0; kb < p.num_kb; ++kb) {
-        if (!mbar_wait<20>(&full_bar[stage], phase, abort_flag)) {
+        if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
           atomicCAS(p.err, 0u, 0x53000000u | static_cast<uint32_t>(stage));
           ok = false;
           break;

@@ -98,7 +98,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity,
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity,
                                                volatile uint32_t *abort_flag) {
   uint32_t ok = 1;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait<40>(bar, parity, abort_flag) ? 1u : 0u;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1u : 0u;
   ok = __shfl_sync(0xffffffffu, ok, 0);
   return ok != 0;
 }
