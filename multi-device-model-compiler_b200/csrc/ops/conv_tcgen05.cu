@@ -227,6 +227,11 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const conv::Para
       const int g_base = nf * Hp + ohf * p.SH;
       const int span = nl * Hp + ohl * p.SH + (p.KH - 1) * p.DH - g_base + 1;
       uint8_t *T = tiles + STAGES * stage_bytes;
+      // the host sized the tiles from an upper bound of span; never write past them
+      if (span * Wp * 64 > p.tile_bytes) {
+        atomicCAS(p.err, 0u, 0x54000000u);
+        ok = false;
+      }
       // this thread's pixel, clamped to the last real one so that every read stays in the tile
       const int mc = min(m, p.M - 1);
       const int nc = mc / p.P, pc = mc - nc * p.P, ohc = pc / p.OW, owc = pc - ohc * p.OW;
