@@ -116,3 +116,17 @@ def test_generated_graph_serves_other_batch_sizes(tmp_path):
         x = rng.standard_normal((rows, 16, 48)).astype(np.float32)
         got = run_model(tmp_path, model, [x], x.shape)
         assert np.max(np.abs(got - oracle.layernorm(x, g, b))) <= 1e-5
+
+
+def test_generated_graph_sharded_over_two_devices(tmp_path):
+    """The runner's --gpus 2 cuts input 0 along dimension 0 and gathers the rows of output 0: a
+    generated module, which reads its batch from the descriptor, needs nothing special."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    rng = np.random.default_rng(9)
+    model, w, b = gm.linear_relu_model(ow, rng, batch=(64, 8), K=32, N=64)
+    x = rng.standard_normal((64, 8, 32)).astype(np.float32)
+    one = run_model(tmp_path, model, [x], (64, 8, 64))
+    two = run_model(tmp_path, model, [x], (64, 8, 64), extra=["--gpus", "2"])
+    assert np.array_equal(one, two)
