@@ -117,6 +117,18 @@ void mgpuSetLastError(int32_t code, const char *what);
 void mgpuRegisterConstant(void *hostPtr, uint64_t sizeBytes);
 void mgpuUnregisterConstant(void *hostPtr);
 
+/* Kernel overrides.  The reference generates a scalar one-element-per-thread kernel for every
+ * elementwise graph (lib/Dialect/Device/IR/GPUOffloadingAttr.cpp:255-313) and the lowered graph
+ * fetches it by name.  After mgpuModuleOverrideKernel(pattern, builtin, rank),
+ * mgpuModuleGetFunction of a matching name (exact, or a prefix ending in '*') returns a handle
+ * that mgpuLaunchKernel routes to the built-in kernel (mdc_add_f32: three operands;
+ * mdc_relu_f32 / mdc_gelu_erf_f32 / mdc_gelu_tanh_f32: two).  The caller keeps passing the
+ * generated kernel's arguments - per operand the expanded memref (allocated, aligned, offset,
+ * sizes[rank], strides[rank]) - and its own grid, which is ignored.  Operands must be
+ * contiguous and of one size, otherwise the launch is refused with a status. */
+void mgpuModuleOverrideKernel(const char *pattern, const char *builtin, int32_t rank);
+void mgpuModuleClearOverrides(void);
+
 /* Pool introspection / control: bytes held from the driver, bytes handed out, and a call
  * that returns every cached block to the driver. */
 uint64_t mgpuPoolReservedBytes(void);

@@ -75,6 +75,8 @@ RUNTIME_SIGNATURES = {
     "mgpuSetDefaultDevice": (None, [_i32]),
     "mgpuTensorMapEncodeTiled": (None, [_vp, C.c_int, _u32, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int]),
     "mgpuTensorMapEncodeTiledMemref": (_vp, [_i64, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
+    "mgpuModuleOverrideKernel": (None, [C.c_char_p, C.c_char_p, _i32]),
+    "mgpuModuleClearOverrides": (None, []),
     "mgpuGetLastError": (_i32, []),
     "mgpuGetLastErrorString": (C.c_char_p, []),
     "mgpuClearLastError": (None, []),

@@ -146,6 +146,23 @@ std::unordered_map<std::string, CUfunction> g_builtin_cache;
 // functions whose dynamic shared memory limit has already been raised to at least this
 std::unordered_map<CUfunction, int32_t> g_smem_limit;
 
+// Kernel overrides: a name pattern of a module kernel generated by the reference toolchain,
+// routed to a built-in kernel.  The generated kernel takes `operands` contiguous memrefs of
+// one rank, each expanded to (allocated, aligned, offset, sizes[rank], strides[rank]).
+struct KernelOverride {
+  std::string pattern;   // exact name, or a prefix followed by '*'
+  std::string builtin;
+  int rank = 1, operands = 3;
+  CUfunction target = nullptr;
+};
+std::vector<KernelOverride *> g_overrides;          // entries are never freed: they are handed out as handles
+std::unordered_set<const void *> g_override_handles;
+
+bool pattern_matches(const std::string &pattern, const char *name) {
+  if (!pattern.empty() && pattern.back() == '*') return strncmp(name, pattern.c_str(), pattern.size() - 1) == 0;
+  return pattern == name;
+}
+
 constexpr int kMaxDevices = 64;
 constexpr size_t kMaxParked = 64;
 struct ObjectCache {
@@ -430,6 +447,12 @@ MDC_API mgpu_function_t mgpuModuleGetFunction(const char *name) {
     g_builtin_cache[name] = reinterpret_cast<CUfunction>(fn);
     return fn;
   }
+  // a module kernel that the caller routed to a built-in one
+  for (KernelOverride *o : g_overrides)
+    if (!o->pattern.empty() && pattern_matches(o->pattern, name)) {
+      if (!o->target) o->target = reinterpret_cast<CUfunction>(mgpuModuleGetFunction(o->builtin.c_str()));
+      return o->target ? o : nullptr;
+    }
   CUfunction function = nullptr;
   if (!g_module) {
     record_error(-1, name, "no such built-in kernel and no module loaded");
@@ -447,6 +470,44 @@ MDC_API void mgpuLaunchKernel(mgpu_function_t function, intptr_t gridX, intptr_t
     return;
   }
   if (!ensure_device() || !driver().ok) return;
+  if (g_override_handles.count(function)) {
+    // The caller passes the generated kernel's arguments: per operand the expanded memref
+    // (allocated, aligned, offset, sizes[rank], strides[rank]).  The built-in takes the data
+    // pointers and the element count and chooses its own launch shape.
+    const KernelOverride *o = static_cast<const KernelOverride *>(function);
+    const int per = 3 + 2 * o->rank;
+    void *ptrs[3] = {nullptr, nullptr, nullptr};
+    int64_t n = 1;
+    for (int op = 0; op < o->operands; ++op) {
+      void **g = params + op * per;
+      char *aligned = *static_cast<char **>(g[1]);
+      const int64_t offset = *static_cast<int64_t *>(g[2]);
+      ptrs[op] = aligned + offset * 4;
+      int64_t count = 1, expect = 1;
+      for (int d = o->rank - 1; d >= 0; --d) {
+        const int64_t size = *static_cast<int64_t *>(g[3 + d]), stride = *static_cast<int64_t *>(g[3 + o->rank + d]);
+        if (size != 1 && stride != expect) {
+          record_error(-1, "mgpuLaunchKernel", "an overridden kernel needs contiguous operands");
+          return;
+        }
+        expect *= size;
+        count *= size;
+      }
+      if (op == 0) n = count;
+      else if (count != n) {
+        record_error(-1, "mgpuLaunchKernel", "an overridden kernel needs operands of one size");
+        return;
+      }
+    }
+    intptr_t grid = 1, block = 1;
+    mgpuBuiltinLaunchShape(n, &grid, &block);
+    void *args3[] = {&ptrs[0], &ptrs[1], &ptrs[2], &n};
+    void *args2[] = {&ptrs[0], &ptrs[1], &n};
+    if (n > 0)
+      DRV_CHECK(driver().LaunchKernel(o->target, (unsigned)grid, 1, 1, (unsigned)block, 1, 1, 0,
+                                      reinterpret_cast<CUstream>(stream), o->operands == 3 ? args3 : args2, nullptr));
+    return;
+  }
   CUfunction fn = reinterpret_cast<CUfunction>(function);
   // Raise the dynamic shared-memory limit only when a launch needs more than the default
   // 48 KiB and more than was already granted (the reference queries the device and sets
@@ -716,4 +777,33 @@ MDC_API void *mgpuTensorMapEncodeTiledMemref(int64_t tensorRank, void *descripto
   if (!RT_CHECK(cudaMalloc(&dmap, sizeof(CUtensorMap)))) return nullptr;
   RT_CHECK(cudaMemcpy(dmap, &map, sizeof(CUtensorMap), cudaMemcpyHostToDevice));
   return dmap;
+}
+
+MDC_API void mgpuModuleOverrideKernel(const char *pattern, const char *builtin, int32_t rank) {
+  if (!pattern || !builtin || rank < 1 || rank > 8) {
+    record_error(-1, "mgpuModuleOverrideKernel", "needs a pattern, a built-in kernel name and a rank of 1-8");
+    return;
+  }
+  const std::string b = builtin;
+  int operands = 0;
+  if (b == "mdc_add_f32") operands = 3;
+  else if (b == "mdc_relu_f32" || b == "mdc_gelu_erf_f32" || b == "mdc_gelu_tanh_f32") operands = 2;
+  if (!operands) {
+    record_error(-1, "mgpuModuleOverrideKernel", "the built-in must be mdc_add_f32, mdc_relu_f32, mdc_gelu_erf_f32 or mdc_gelu_tanh_f32");
+    return;
+  }
+  for (KernelOverride *o : g_overrides)
+    if (o->pattern == pattern) {  // redefinition
+      o->builtin = b, o->rank = rank, o->operands = operands, o->target = nullptr;
+      return;
+    }
+  KernelOverride *o = new KernelOverride;
+  o->pattern = pattern, o->builtin = b, o->rank = rank, o->operands = operands;
+  g_overrides.push_back(o);
+  g_override_handles.insert(o);
+}
+
+MDC_API void mgpuModuleClearOverrides(void) {
+  // handles already given out stay valid objects; they only stop being matched
+  for (KernelOverride *o : g_overrides) o->pattern.clear();
 }

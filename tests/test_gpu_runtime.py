@@ -99,3 +99,121 @@ def test_pageable_copy_rate_report(m, capsys):
     assert out[0] == 1 and out[-1] == 1
     with capsys.disabled():
         print(f"\n[pageable mgpuMemcpy, 256 MiB] h2d {rates['h2d']:.1f} GB/s, d2h {rates['d2h']:.1f} GB/s")
+
+
+# A kernel in the form the reference's toolchain emits for an elementwise graph: PTX for sm_70
+# (lib/Utils/CompileOptions.cpp:107-123) whose arguments are the expanded memref descriptors
+# (allocated pointer, aligned pointer, offset, size, stride per operand).  The driver JIT-compiles
+# it for sm_100 when mgpuModuleFileLoad hands the file to cuModuleLoad.
+_ADD_PTX = """
+.version 7.0
+.target sm_70
+.address_size 64
+
+.visible .entry main_graph_kernel(
+    .param .u64 a_alloc, .param .u64 a_aligned, .param .u64 a_off, .param .u64 a_size, .param .u64 a_stride,
+    .param .u64 b_alloc, .param .u64 b_aligned, .param .u64 b_off, .param .u64 b_size, .param .u64 b_stride,
+    .param .u64 c_alloc, .param .u64 c_aligned, .param .u64 c_off, .param .u64 c_size, .param .u64 c_stride)
+{
+    .reg .pred p;
+    .reg .b32 r<5>;
+    .reg .b64 rd<12>;
+    .reg .f32 f<4>;
+    ld.param.u64 rd1, [a_aligned];
+    ld.param.u64 rd2, [b_aligned];
+    ld.param.u64 rd3, [c_aligned];
+    ld.param.u64 rd4, [a_size];
+    mov.u32 r1, %ctaid.x;
+    mov.u32 r2, %ntid.x;
+    mov.u32 r3, %tid.x;
+    mad.lo.s32 r4, r1, r2, r3;
+    cvt.u64.u32 rd5, r4;
+    setp.ge.u64 p, rd5, rd4;
+    @p bra DONE;
+    cvta.to.global.u64 rd1, rd1;
+    cvta.to.global.u64 rd2, rd2;
+    cvta.to.global.u64 rd3, rd3;
+    shl.b64 rd6, rd5, 2;
+    add.s64 rd7, rd1, rd6;
+    add.s64 rd8, rd2, rd6;
+    add.s64 rd9, rd3, rd6;
+    ld.global.f32 f1, [rd7];
+    ld.global.f32 f2, [rd8];
+    add.f32 f3, f1, f2;
+    st.global.f32 [rd9], f3;
+DONE:
+    ret;
+}
+"""
+
+
+def test_ptx_module_from_the_reference_toolchain_loads_and_runs(m, tmp_path):
+    rt = m.runtime()
+    path = tmp_path / "ops.ptx"
+    path.write_text(_ADD_PTX)
+    n = 100_003
+    rng = np.random.default_rng(5)
+    a, b = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    da, db, dc = m.to_device(a), m.to_device(b), m.DeviceBuffer(n * 4)
+    rt.mgpuModuleFileLoad(str(path).encode())
+    m.check("mgpuModuleFileLoad")
+    fn = rt.mgpuModuleGetFunction(b"main_graph_kernel")
+    assert fn
+    vals = []
+    for ptr in (da.ptr, db.ptr, dc.ptr):
+        vals += [ptr, ptr, 0, n, 1]  # allocated, aligned, offset, size, stride
+    cells = [C.c_uint64(v) for v in vals]
+    params = (C.c_void_p * len(cells))(*[C.cast(C.pointer(c), C.c_void_p) for c in cells])
+    block = 256
+    rt.mgpuLaunchKernel(fn, (n + block - 1) // block, 1, 1, block, 1, 1, 0, None, params, None)
+    rt.mgpuStreamSynchronize(None)
+    m.check("launch of the loaded kernel")
+    assert np.array_equal(m.to_host(dc, (n,), np.float32), a + b)
+    # the built-in registry still answers while a module is loaded, and after it is unloaded
+    assert rt.mgpuModuleGetFunction(b"mdc_add_f32")
+    rt.mgpuModuleUnload()
+    assert rt.mgpuModuleGetFunction(b"mdc_add_f32")
+    m.check("module unload")
+
+
+def test_kernel_override_routes_a_generated_kernel_to_the_builtin(m, tmp_path):
+    """The module's kernel here SUBTRACTS, so the result tells which kernel ran: with the
+    override in place the built-in Add runs on the generated kernel's own argument list."""
+    rt = m.runtime()
+    path = tmp_path / "ops.ptx"
+    path.write_text(_ADD_PTX.replace("add.f32 f3, f1, f2;", "sub.f32 f3, f1, f2;"))
+    n = 70_001
+    rng = np.random.default_rng(6)
+    a, b = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    da, db, dc = m.to_device(a), m.to_device(b), m.DeviceBuffer(n * 4)
+    rt.mgpuModuleFileLoad(str(path).encode())
+    vals = []
+    for ptr in (da.ptr, db.ptr, dc.ptr):
+        vals += [ptr, ptr, 0, n, 1]
+    cells = [C.c_uint64(v) for v in vals]
+    params = (C.c_void_p * len(cells))(*[C.cast(C.pointer(c), C.c_void_p) for c in cells])
+
+    def launch():
+        fn = rt.mgpuModuleGetFunction(b"main_graph_kernel")
+        assert fn
+        rt.mgpuLaunchKernel(fn, (n + 255) // 256, 1, 1, 256, 1, 1, 0, None, params, None)
+        rt.mgpuStreamSynchronize(None)
+        m.check("launch")
+        return m.to_host(dc, (n,), np.float32)
+
+    assert np.array_equal(launch(), a - b)
+    rt.mgpuModuleOverrideKernel(b"main_graph_ker*", b"mdc_add_f32", 1)
+    assert np.array_equal(launch(), a + b)
+    # a non-contiguous operand is refused, not silently mishandled
+    cells[4].value = 2
+    fn = rt.mgpuModuleGetFunction(b"main_graph_kernel")
+    rt.mgpuLaunchKernel(fn, 1, 1, 1, 256, 1, 1, 0, None, params, None)
+    assert rt.mgpuGetLastError() != 0
+    rt.mgpuClearLastError()
+    cells[4].value = 1
+    rt.mgpuModuleClearOverrides()
+    assert np.array_equal(launch(), a - b)
+    rt.mgpuModuleOverrideKernel(b"x", b"no_such_builtin", 1)
+    assert rt.mgpuGetLastError() != 0
+    rt.mgpuClearLastError()
+    rt.mgpuModuleUnload()
