@@ -1,7 +1,7 @@
 """Generates tests/golden/reference_models.npz.
 
 Run once, in a container that has the reference checkout:
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <checkout of the reference project>
 It imports the reference's own PyTorch model definitions
 (benchmark/PyTorch/Models/LLM.py:5-21 `Decoder`, benchmark/PyTorch/Models/Linear.py:5-19
 `Linear`), runs them in fp32 on seeded inputs and stores inputs, weights (transposed to the
@@ -155,4 +155,6 @@ def cnn_fixtures():
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <checkout of the reference project>")
+    main(sys.argv[1])
