@@ -172,26 +172,49 @@ cast_pad_rows(const float *__restrict__ src, T16 *__restrict__ dst, int64_t R, i
 }
 
 // weight fp32 [K, N] (N contiguous) -> 16-bit [N, Kp] (K contiguous), zero padded to Kp.
-// 32x32 tiles through shared memory so both the reads and the writes are coalesced.
+// 64 x 64 tiles through shared memory: reads are 16-byte vectors along n (whole lines of w),
+// writes are 16-byte vectors of eight 16-bit values along k (whole lines of out).
 template <typename T16>
 __global__ void __launch_bounds__(256)
-pack_weight_kernel(const float *__restrict__ w, T16 *__restrict__ out, int64_t K, int64_t N, int64_t Kp) {
-  __shared__ float tile[32][33];
-  const int64_t k0 = static_cast<int64_t>(blockIdx.y) * 32;
-  const int64_t n0 = static_cast<int64_t>(blockIdx.x) * 32;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+pack_weight_kernel(const float *__restrict__ w, T16 *__restrict__ out, int64_t K, int64_t N, int64_t Kp, int vec_ok) {
+  __shared__ float tile[64][65];
+  const int64_t k0 = static_cast<int64_t>(blockIdx.y) * 64;
+  const int64_t n0 = static_cast<int64_t>(blockIdx.x) * 64;
+  {
+    const int c4 = (threadIdx.x & 15) * 4, r0 = threadIdx.x >> 4;  // 16 threads per k-row, 16 rows per pass
 #pragma unroll
-  for (int r = ty; r < 32; r += 8) {
-    const int64_t k = k0 + r, n = n0 + tx;
-    tile[r][tx] = (k < K && n < N) ? w[k * N + n] : 0.f;
+    for (int r = r0; r < 64; r += 16) {
+      const int64_t k = k0 + r, n = n0 + c4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (k < K) {
+        if (vec_ok && n + 3 < N) {
+          v = __ldg(reinterpret_cast<const float4 *>(w + k * N + n));
+        } else {
+          if (n < N) v.x = w[k * N + n];
+          if (n + 1 < N) v.y = w[k * N + n + 1];
+          if (n + 2 < N) v.z = w[k * N + n + 2];
+          if (n + 3 < N) v.w = w[k * N + n + 3];
+        }
+      }
+      tile[r][c4] = v.x, tile[r][c4 + 1] = v.y, tile[r][c4 + 2] = v.z, tile[r][c4 + 3] = v.w;
+    }
   }
   __syncthreads();
+  {
+    const int kg = (threadIdx.x & 7) * 8, r0 = threadIdx.x >> 3;  // 8 threads per n-row, 32 rows per pass
 #pragma unroll
-  for (int r = ty; r < 32; r += 8) {
-    const int64_t n = n0 + r, k = k0 + tx;
-    if (n < N && k < Kp) out[n * Kp + k] = from_f32<T16>(tile[tx][r]);
+    for (int r = r0; r < 64; r += 32) {
+      const int64_t n = n0 + r, k = k0 + kg;
+      if (n < N && k < Kp) {  // Kp is a multiple of 8: a group of eight is inside or outside as a whole
+        __align__(16) T16 h[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) h[e] = from_f32<T16>(tile[kg + e][r]);
+        *reinterpret_cast<uint4 *>(out + n * Kp + k) = *reinterpret_cast<const uint4 *>(h);
+      }
+    }
   }
 }
+
 
 }  // namespace mdc
 
@@ -351,10 +374,12 @@ MDC_API void mgpuPackWeight(const float *w, void *packed, int64_t K, int64_t N, 
   }
   if (!device_info().ok) return;
   const int64_t Kp = (K + 7) / 8 * 8;
-  dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((Kp + 31) / 32));
+  if (reinterpret_cast<uintptr_t>(packed) & 15u) { fail("mgpuPackWeight: the packed buffer must be 16-byte aligned"); return; }
+  dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((Kp + 63) / 64));
+  const int vec_ok = (N % 4 == 0) && !(reinterpret_cast<uintptr_t>(w) & 15u);
   if (dtype == MGPU_DTYPE_F16)
-    pack_weight_kernel<__half><<<grid, 256, 0, as_stream(stream)>>>(w, (__half *)packed, K, N, Kp);
+    pack_weight_kernel<__half><<<grid, 256, 0, as_stream(stream)>>>(w, (__half *)packed, K, N, Kp, vec_ok);
   else
-    pack_weight_kernel<__nv_bfloat16><<<grid, 256, 0, as_stream(stream)>>>(w, (__nv_bfloat16 *)packed, K, N, Kp);
+    pack_weight_kernel<__nv_bfloat16><<<grid, 256, 0, as_stream(stream)>>>(w, (__nv_bfloat16 *)packed, K, N, Kp, vec_ok);
   launched("mdc_pack_weight");
 }
