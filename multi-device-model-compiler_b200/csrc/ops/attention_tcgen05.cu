@@ -247,6 +247,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
         int ncol = it.kv_end - j * BKV;
         if (p.causal) ncol = min(ncol, q_local + 1 - j * BKV);
         ncol = max(min(ncol, BKV), 0);
+        // every row of this warp sees the whole tile: no per-element masking
+        const bool full_tile = __all_sync(0xffffffffu, ncol == BKV);
         // pass 1: row maximum
         float m_tile = -INFINITY;
 #pragma unroll 1
@@ -254,9 +256,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
           uint32_t s[32];
           tmem_ld_32x32(tmem_base + lane_addr + S_COL + c * 32, s);
           tmem_ld_wait_regs(s);
+          if (full_tile) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < ncol) m_tile = fmaxf(m_tile, __uint_as_float(s[i]));
+            for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(s[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i < ncol) m_tile = fmaxf(m_tile, __uint_as_float(s[i]));
+          }
         }
         const float m_new = fmaxf(m_run, m_tile);
         // rows with no visible key yet keep m = -inf; use 0 as the reference point then
@@ -272,13 +279,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
           tmem_ld_32x32(tmem_base + lane_addr + S_COL + c * 32, s);
           tmem_ld_wait_regs(s);
           uint32_t packed[16];
+          if (full_tile) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p0 = 0.f, p1 = 0.f;
-            if (c * 32 + i < ncol) p0 = ex2_fast(fmaf(__uint_as_float(s[i]), p.scale_log2e, -mc));
-            if (c * 32 + i + 1 < ncol) p1 = ex2_fast(fmaf(__uint_as_float(s[i + 1]), p.scale_log2e, -mc));
-            l_tile += p0 + p1;
-            packed[i >> 1] = pack16<T16>(p0, p1);
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = ex2_fast(fmaf(__uint_as_float(s[i]), p.scale_log2e, -mc));
+              const float p1 = ex2_fast(fmaf(__uint_as_float(s[i + 1]), p.scale_log2e, -mc));
+              l_tile += p0 + p1;
+              packed[i >> 1] = pack16<T16>(p0, p1);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float p0 = 0.f, p1 = 0.f;
+              if (c * 32 + i < ncol) p0 = ex2_fast(fmaf(__uint_as_float(s[i]), p.scale_log2e, -mc));
+              if (c * 32 + i + 1 < ncol) p1 = ex2_fast(fmaf(__uint_as_float(s[i + 1]), p.scale_log2e, -mc));
+              l_tile += p0 + p1;
+              packed[i >> 1] = pack16<T16>(p0, p1);
+            }
           }
           tmem_st_32x16(tmem_base + lane_addr + P_COL + c * 16, packed);
         }
