@@ -251,15 +251,28 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
         const bool full_tile = __all_sync(0xffffffffu, ncol == BKV);
         // pass 1: row maximum
         float m_tile = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < BKV / 32; ++c) {
-          uint32_t s[32];
-          tmem_ld_32x32(tmem_base + lane_addr + S_COL + c * 32, s);
-          tmem_ld_wait_regs(s);
-          if (full_tile) {
+        if (full_tile) {
+          // 16 columns at a time, the next load in flight while the current piece is reduced
+          uint32_t sa[16], sb[16];
+          const uint32_t s_addr = tmem_base + lane_addr + S_COL;
+          tmem_ld_32x16(s_addr, sa);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, __uint_as_float(s[i]));
-          } else {
+          for (int c = 0; c < BKV / 16; c += 2) {
+            tmem_ld_wait_regs(sa);
+            tmem_ld_32x16(s_addr + (c + 1) * 16, sb);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) m_tile = fmaxf(m_tile, __uint_as_float(sa[i]));
+            tmem_ld_wait_regs(sb);
+            if (c + 2 < BKV / 16) tmem_ld_32x16(s_addr + (c + 2) * 16, sa);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) m_tile = fmaxf(m_tile, __uint_as_float(sb[i]));
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < BKV / 32; ++c) {
+            uint32_t s[32];
+            tmem_ld_32x32(tmem_base + lane_addr + S_COL + c * 32, s);
+            tmem_ld_wait_regs(s);
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (c * 32 + i < ncol) m_tile = fmaxf(m_tile, __uint_as_float(s[i]));
@@ -273,21 +286,43 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
         // goes to columns [16c, 16c+16), over S columns this thread has already consumed
         float l_tile = 0.f;
         const float mc = m_ref * p.scale_log2e;
-#pragma unroll 1
-        for (int c = 0; c < BKV / 32; ++c) {
-          uint32_t s[32];
-          tmem_ld_32x32(tmem_base + lane_addr + S_COL + c * 32, s);
-          tmem_ld_wait_regs(s);
-          uint32_t packed[16];
-          if (full_tile) {
+        if (full_tile) {
+          // the same pipelining; two 16-column pieces of S make one 16-register piece of P
+          uint32_t sa[16], sb[16];
+          const uint32_t s_addr = tmem_base + lane_addr + S_COL;
+          tmem_ld_32x16(s_addr, sa);
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float p0 = ex2_fast(fmaf(__uint_as_float(s[i]), p.scale_log2e, -mc));
-              const float p1 = ex2_fast(fmaf(__uint_as_float(s[i + 1]), p.scale_log2e, -mc));
+          for (int c = 0; c < BKV / 16; c += 2) {
+            uint32_t packed[16];
+            tmem_ld_wait_regs(sa);
+            tmem_ld_32x16(s_addr + (c + 1) * 16, sb);
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+              const float p0 = ex2_fast(fmaf(__uint_as_float(sa[i]), p.scale_log2e, -mc));
+              const float p1 = ex2_fast(fmaf(__uint_as_float(sa[i + 1]), p.scale_log2e, -mc));
               l_tile += p0 + p1;
               packed[i >> 1] = pack16<T16>(p0, p1);
             }
-          } else {
+            tmem_ld_wait_regs(sb);
+            // the P piece below overwrites S columns [8c, 8c + 16): all of them have been read
+            // (this thread is past column 16c + 32), so the next S load may start first
+            if (c + 2 < BKV / 16) tmem_ld_32x16(s_addr + (c + 2) * 16, sa);
+#pragma unroll
+            for (int i = 0; i < 16; i += 2) {
+              const float p0 = ex2_fast(fmaf(__uint_as_float(sb[i]), p.scale_log2e, -mc));
+              const float p1 = ex2_fast(fmaf(__uint_as_float(sb[i + 1]), p.scale_log2e, -mc));
+              l_tile += p0 + p1;
+              packed[8 + (i >> 1)] = pack16<T16>(p0, p1);
+            }
+            tmem_st_32x16(tmem_base + lane_addr + P_COL + (c / 2) * 16, packed);
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < BKV / 32; ++c) {
+            uint32_t s[32];
+            tmem_ld_32x32(tmem_base + lane_addr + S_COL + c * 32, s);
+            tmem_ld_wait_regs(s);
+            uint32_t packed[16];
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
               float p0 = 0.f, p1 = 0.f;
@@ -296,8 +331,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
               l_tile += p0 + p1;
               packed[i >> 1] = pack16<T16>(p0, p1);
             }
+            tmem_st_32x16(tmem_base + lane_addr + P_COL + c * 16, packed);
           }
-          tmem_st_32x16(tmem_base + lane_addr + P_COL + c * 16, packed);
         }
         l_run = fmaf(l_run, alpha, l_tile);
         m_run = m_new;
