@@ -3,11 +3,12 @@
 // Replaces generalAddBiasResidualLayerNormOpt2 (lib/Kernels/GPU/LayerNorm.cu:138-260),
 // which keeps one block per row, stages the row in shared memory as half2 and derives the
 // variance from E[x^2] - mean^2.  Here one WARP owns a row: the row is read from HBM once
-// with 128-bit loads straight into registers, every lane forms a Welford (count, mean, M2)
-// triple over its own elements, the 32 triples are merged with Chan's formula through
-// warp shuffles, and the normalised row is written with 128-bit stores.  No shared memory,
-// no block barrier, exactly one HBM read and one HBM write per element: the kernel is
-// bound by HBM bandwidth (8 bytes per element for fp32 in/out).
+// with 128-bit loads straight into registers, the statistics are an exact two-pass
+// computation over the registers (the mean by one shuffle butterfly, the centred sum of squares
+// by a second one), and the normalised row is written with 128-bit stores.  No shared memory,
+// no block barrier, exactly one HBM read and one HBM write per element: fp32 rows are bound by
+// HBM bandwidth (8 bytes per element); the shorter 16-bit rows are bound by instruction issue,
+// which is why the statistics avoid anything costlier than adds and shuffles.
 #include "ops_common.h"
 
 namespace mdc {
@@ -114,6 +115,7 @@ layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residua
   int64_t row = static_cast<int64_t>(blockIdx.x) * kLnWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= m) return;
   const int nchunks = n / EPC;
+  const float inv_n = 1.f / static_cast<float>(n);
   constexpr bool has_res = RES;
   constexpr bool kPrefetch = sizeof(TIn) == 2;
 
@@ -162,47 +164,32 @@ layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residua
     const int64_t next = kPrefetch ? row + total_warps : m;
     if (next < m) fetch(next);
 
-    // per-lane Welford triple (count, mean, M2) over the lane's own elements
-    float cnt = 0.f, mean = 0.f, m2 = 0.f;
-    {
-      float s = 0.f;
+    // exact two-pass statistics across the warp: the mean first (one butterfly), then the
+    // centred sum of squares (a second one).  Every lane ends with the same bits, because the
+    // two partners of a butterfly step add the same two numbers.
+    float sum = 0.f;
 #pragma unroll
-      for (int i = 0; i < MAXI; ++i)
-        if (lane + 32 * i < nchunks) {
+    for (int i = 0; i < MAXI; ++i)
+      if (lane + 32 * i < nchunks) {
 #pragma unroll
-          for (int e = 0; e < EPC; ++e) s += v[i][e];
-          cnt += static_cast<float>(EPC);
-        }
-      mean = cnt > 0.f ? s / cnt : 0.f;
-#pragma unroll
-      for (int i = 0; i < MAXI; ++i)
-        if (lane + 32 * i < nchunks) {
-#pragma unroll
-          for (int e = 0; e < EPC; ++e) {
-            const float d = v[i][e] - mean;
-            m2 = fmaf(d, d, m2);
-          }
-        }
-    }
-    // Chan's merge of two Welford triples, butterfly over the warp
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      const float cnt_o = __shfl_xor_sync(0xffffffffu, cnt, off);
-      const float mean_o = __shfl_xor_sync(0xffffffffu, mean, off);
-      const float m2_o = __shfl_xor_sync(0xffffffffu, m2, off);
-      const float tot = cnt + cnt_o;
-      if (tot > 0.f) {
-        const float delta = mean_o - mean;
-        const float w = cnt_o / tot;
-        mean = fmaf(delta, w, mean);
-        m2 = m2 + m2_o + delta * delta * cnt * w;
+        for (int e = 0; e < EPC; ++e) sum += v[i][e];
       }
-      cnt = tot;
-    }
-    // the two sides of a merge round differently in the last bit: take lane 0's result
-    mean = __shfl_sync(0xffffffffu, mean, 0);
-    m2 = __shfl_sync(0xffffffffu, m2, 0);
-    const float rstd = rsqrtf(m2 / static_cast<float>(n) + eps);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    const float mean = sum * inv_n;
+    float m2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXI; ++i)
+      if (lane + 32 * i < nchunks) {
+#pragma unroll
+        for (int e = 0; e < EPC; ++e) {
+          v[i][e] -= mean;  // the centred value is what the output needs too
+          m2 = fmaf(v[i][e], v[i][e], m2);
+        }
+      }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m2 += __shfl_xor_sync(0xffffffffu, m2, off);
+    const float rstd = rsqrtf(fmaf(m2, inv_n, eps));
 
 #pragma unroll
     for (int i = 0; i < MAXI; ++i) {
@@ -214,10 +201,10 @@ layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residua
           float4 g = make_float4(1.f, 1.f, 1.f, 1.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
           if (gamma) g = __ldg(reinterpret_cast<const float4 *>(gamma) + c * (EPC / 4) + e4);
           if (beta) b = __ldg(reinterpret_cast<const float4 *>(beta) + c * (EPC / 4) + e4);
-          o[4 * e4 + 0] = fmaf((v[i][4 * e4 + 0] - mean) * rstd, g.x, b.x);
-          o[4 * e4 + 1] = fmaf((v[i][4 * e4 + 1] - mean) * rstd, g.y, b.y);
-          o[4 * e4 + 2] = fmaf((v[i][4 * e4 + 2] - mean) * rstd, g.z, b.z);
-          o[4 * e4 + 3] = fmaf((v[i][4 * e4 + 3] - mean) * rstd, g.w, b.w);
+          o[4 * e4 + 0] = fmaf(v[i][4 * e4 + 0] * rstd, g.x, b.x);
+          o[4 * e4 + 1] = fmaf(v[i][4 * e4 + 1] * rstd, g.y, b.y);
+          o[4 * e4 + 2] = fmaf(v[i][4 * e4 + 2] * rstd, g.z, b.z);
+          o[4 * e4 + 3] = fmaf(v[i][4 * e4 + 3] * rstd, g.w, b.w);
         }
         store_vec<TOut, EPC>(y + row * n + static_cast<int64_t>(c) * EPC, o);
       }
