@@ -144,34 +144,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
-// Two fp32 lanes per instruction (fma.rn.f32x2 and friends, sm_100): the epilogue's
-// arithmetic is issue-bound next to the tensor pipe, and this halves its FMA / MUL count.
-struct F2 {
-  uint64_t v;
-};
-__device__ __forceinline__ F2 f2(float a, float b) {
-  F2 r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ void f2_get(F2 x, float &a, float &b) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(x.v));
-}
-__device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) {
-  F2 d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d.v) : "l"(a.v), "l"(b.v), "l"(c.v));
-  return d;
-}
-__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) {
-  F2 d;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d.v) : "l"(a.v), "l"(b.v));
-  return d;
-}
-__device__ __forceinline__ F2 f2_add(F2 a, F2 b) {
-  F2 d;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d.v) : "l"(a.v), "l"(b.v));
-  return d;
-}
+using ptx::F2;
+using ptx::f2;
+using ptx::f2_add;
+using ptx::f2_fma;
+using ptx::f2_get;
+using ptx::f2_mul;
 
 // Exact-erf GELU on two values at once: 0.5 v (1 + sign(v) erf(|v| / sqrt 2)) with
 // y = |v| / sqrt(2) * sqrt(log2 e), so that exp(-x^2) = 2^(-y^2), and p rescaled to match.

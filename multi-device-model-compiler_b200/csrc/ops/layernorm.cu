@@ -103,8 +103,11 @@ constexpr int kLnWarpsPerBlock = 4;
 // (short 16-bit rows would otherwise leave too few bytes in flight per SM).  n must be a
 // multiple of EPC, rows 16-byte aligned, and n <= 32 * MAXI * EPC.  Lane l owns chunks
 // l, l+32, ... (coalesced 512-byte warp accesses).
-template <typename TIn, typename TOut, int MAXI, bool RES>
-__global__ void __launch_bounds__(kLnWarpsPerBlock * 32, (MAXI > 8 || sizeof(TIn) == 4) ? 2 : (RES ? 4 : 6))
+// FULL: the row is exactly 32 * MAXI chunks, so no lane ever skips a chunk and the per-chunk
+// tests (and the instructions of chunks that would be predicated off) disappear.
+template <typename TIn, typename TOut, int MAXI, bool RES, bool FULL>
+__global__ void __launch_bounds__(kLnWarpsPerBlock * 32,
+                                  (MAXI >= 8 || sizeof(TIn) == 4) ? 2 : ((RES || (FULL && MAXI >= 4)) ? 4 : 6))
 layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residual,
                       const float *__restrict__ gamma, const float *__restrict__ beta,
                       TIn *__restrict__ sum_out, TOut *__restrict__ y, float eps, int64_t m, int n) {
@@ -125,14 +128,14 @@ layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residua
 #pragma unroll
     for (int i = 0; i < MAXI; ++i) {
       const int c = lane + 32 * i;
-      if (c < nchunks) raw[i] = __ldcs(xr + c);
+      if (FULL || c < nchunks) raw[i] = __ldcs(xr + c);
     }
     if constexpr (has_res) {
       const uint4 *rr = reinterpret_cast<const uint4 *>(residual + rw * n);
 #pragma unroll
       for (int i = 0; i < MAXI; ++i) {
         const int c = lane + 32 * i;
-        if (c < nchunks) raw_res[i] = __ldcs(rr + c);
+        if (FULL || c < nchunks) raw_res[i] = __ldcs(rr + c);
       }
     }
   };
@@ -143,13 +146,13 @@ layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residua
 #pragma unroll
     for (int i = 0; i < MAXI; ++i) {
       const int c = lane + 32 * i;
-      if (c < nchunks) LnTraits<TIn>::unpack(raw[i], v[i]);
+      if (FULL || c < nchunks) LnTraits<TIn>::unpack(raw[i], v[i]);
     }
     if constexpr (has_res) {
 #pragma unroll
       for (int i = 0; i < MAXI; ++i) {
         const int c = lane + 32 * i;
-        if (c < nchunks) {
+        if (FULL || c < nchunks) {
           float r[EPC];
           LnTraits<TIn>::unpack(raw_res[i], r);
 #pragma unroll
@@ -170,7 +173,7 @@ layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residua
     float sum = 0.f;
 #pragma unroll
     for (int i = 0; i < MAXI; ++i)
-      if (lane + 32 * i < nchunks) {
+      if (FULL || lane + 32 * i < nchunks) {
 #pragma unroll
         for (int e = 0; e < EPC; ++e) sum += v[i][e];
       }
@@ -180,7 +183,7 @@ layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residua
     float m2 = 0.f;
 #pragma unroll
     for (int i = 0; i < MAXI; ++i)
-      if (lane + 32 * i < nchunks) {
+      if (FULL || lane + 32 * i < nchunks) {
 #pragma unroll
         for (int e = 0; e < EPC; ++e) {
           v[i][e] -= mean;  // the centred value is what the output needs too
@@ -194,7 +197,7 @@ layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residua
 #pragma unroll
     for (int i = 0; i < MAXI; ++i) {
       const int c = lane + 32 * i;
-      if (c < nchunks) {
+      if (FULL || c < nchunks) {
         float o[EPC];
 #pragma unroll
         for (int e4 = 0; e4 < EPC / 4; ++e4) {
@@ -281,7 +284,8 @@ static void launch_layernorm(const void *x, const void *residual, const float *g
   TIn *so = static_cast<TIn *>(sum_out);
   TOut *yo = static_cast<TOut *>(y);
   if (vec_ok) {
-    const int per_lane = static_cast<int>((n / EPC + 31) / 32);
+    const int nchunks_host = static_cast<int>(n / EPC);
+    const int per_lane = (nchunks_host + 31) / 32;
     // persistent: at most 16 blocks of 4 warps per SM, each warp walking several rows
     const int64_t blocks_needed = (m + kLnWarpsPerBlock - 1) / kLnWarpsPerBlock;
     const int64_t blocks_cap = static_cast<int64_t>(device_info().sms) * 16;
@@ -289,12 +293,17 @@ static void launch_layernorm(const void *x, const void *residual, const float *g
         (sizeof(TIn) == 2 && blocks_needed > blocks_cap) ? blocks_cap : blocks_needed);
     const int threads = kLnWarpsPerBlock * 32;
     const int ni = static_cast<int>(n);
-#define MDC_LN_LAUNCH(MAXI_)                                                                          \
+#define MDC_LN_LAUNCH2(MAXI_, FULL_)                                                                  \
   do {                                                                                            \
     if (ri)                                                                                       \
-      check_cuda(launch_chain(layernorm_warp_kernel<TIn, TOut, MAXI_, true>, dim3(grid), dim3(threads), 0, s, 1, xi, ri, gamma, beta, so, yo, eps, m, ni), "launch layernorm");  \
+      check_cuda(launch_chain(layernorm_warp_kernel<TIn, TOut, MAXI_, true, FULL_>, dim3(grid), dim3(threads), 0, s, 1, xi, ri, gamma, beta, so, yo, eps, m, ni), "launch layernorm");  \
     else                                                                                          \
-      check_cuda(launch_chain(layernorm_warp_kernel<TIn, TOut, MAXI_, false>, dim3(grid), dim3(threads), 0, s, 1, xi, ri, gamma, beta, so, yo, eps, m, ni), "launch layernorm"); \
+      check_cuda(launch_chain(layernorm_warp_kernel<TIn, TOut, MAXI_, false, FULL_>, dim3(grid), dim3(threads), 0, s, 1, xi, ri, gamma, beta, so, yo, eps, m, ni), "launch layernorm"); \
+  } while (0)
+#define MDC_LN_LAUNCH(MAXI_)                                                                          \
+  do {                                                                                            \
+    if (nchunks_host == 32 * (MAXI_)) MDC_LN_LAUNCH2(MAXI_, true);                                \
+    else MDC_LN_LAUNCH2(MAXI_, false);                                                            \
   } while (0)
     if (per_lane <= 2) MDC_LN_LAUNCH(2);
     else if (per_lane <= 4) MDC_LN_LAUNCH(4);
@@ -302,6 +311,7 @@ static void launch_layernorm(const void *x, const void *residual, const float *g
     else if (per_lane <= 8) MDC_LN_LAUNCH(8);
     else MDC_LN_LAUNCH(16);
 #undef MDC_LN_LAUNCH
+#undef MDC_LN_LAUNCH2
     launched("layernorm_warp_kernel");
   } else {
     const size_t smem = static_cast<size_t>(n) * sizeof(float);

@@ -346,5 +346,35 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t m, uint32_t n, bo
          ((m >> 4) << 24);
 }
 
+// Two fp32 lanes per instruction (fma.rn.f32x2 and friends, sm_100): kernels whose
+// arithmetic is bound by instruction issue halve their FMA / MUL / ADD count with these.
+struct F2 {
+  uint64_t v;
+};
+__device__ __forceinline__ F2 f2(float a, float b) {
+  F2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_get(F2 x, float &a, float &b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(x.v));
+}
+__device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) {
+  F2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d.v) : "l"(a.v), "l"(b.v), "l"(c.v));
+  return d;
+}
+__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) {
+  F2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d.v) : "l"(a.v), "l"(b.v));
+  return d;
+}
+__device__ __forceinline__ F2 f2_add(F2 a, F2 b) {
+  F2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d.v) : "l"(a.v), "l"(b.v));
+  return d;
+}
+
+
 }  // namespace ptx
 }  // namespace mdc
