@@ -699,7 +699,15 @@ static int gemm_grid(const GemmParams &p, int sms) {
   const int64_t tiles = static_cast<int64_t>((p.num_m_blocks + cg - 1) / cg) * p.num_n_blocks;
   if (tiles > 0x7fffffff) return -1;
   const int64_t max_workers = sms / cg;
-  return static_cast<int>((tiles < max_workers ? tiles : max_workers) * cg);
+  if (tiles <= max_workers) return static_cast<int>(tiles * cg);
+  // The kernel takes ceil(tiles / workers) rounds whatever the last round holds.  Use the
+  // fewest workers that still finish in that many rounds: the SMs left idle draw no power,
+  // which the power-capped tensor cores of the others turn into clock (MDC_GEMM_EVEN_WAVES=0
+  // uses every SM).
+  static const bool even = !(getenv("MDC_GEMM_EVEN_WAVES") && atoi(getenv("MDC_GEMM_EVEN_WAVES")) == 0);
+  const int64_t rounds = (tiles + max_workers - 1) / max_workers;
+  const int64_t workers = even ? (tiles + rounds - 1) / rounds : max_workers;
+  return static_cast<int>(workers * cg);
 }
 
 }  // namespace mdc
