@@ -302,10 +302,11 @@ static void launch_layernorm(const void *x, const void *residual, const float *g
   } while (0)
 #define MDC_LN_LAUNCH(MAXI_)                                                                          \
   do {                                                                                            \
-    if (nchunks_host == 32 * (MAXI_)) MDC_LN_LAUNCH2(MAXI_, true);                                \
+    if (nchunks_host == 32 * (MAXI_) && !(sizeof(TIn) == 2 && (MAXI_) == 3)) MDC_LN_LAUNCH2(MAXI_, true); \
     else MDC_LN_LAUNCH2(MAXI_, false);                                                            \
   } while (0)
     if (per_lane <= 2) MDC_LN_LAUNCH(2);
+    else if (per_lane <= 3) MDC_LN_LAUNCH(3);
     else if (per_lane <= 4) MDC_LN_LAUNCH(4);
     else if (per_lane <= 6) MDC_LN_LAUNCH(6);
     else if (per_lane <= 8) MDC_LN_LAUNCH(8);
