@@ -56,6 +56,26 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def use_blas(on: bool = True) -> bool:
+    """Timed CPU baseline only: route the oracle's Gemm through cblas_sgemm of the OpenBLAS
+    bundled with numpy (when the wheel carries one).  Returns whether it is in use."""
+    import glob
+    if not on:
+        lib().oracle_use_blas(None, None)
+        return False
+    libs = glob.glob(os.path.join(os.path.dirname(np.__file__), "..", "numpy.libs", "libscipy_openblas64_*.so"))
+    for path in libs:
+        if lib().oracle_use_blas(os.path.abspath(path).encode(), b"scipy_cblas_sgemm64_"):
+            return True
+    return False
+
+
+def gemm_kernel_name() -> str:
+    if lib().oracle_blas_in_use():
+        return "cblas_sgemm of the OpenBLAS bundled with numpy"
+    return "own AVX2/FMA 4x32 register-panel loop (OpenMP)"
+
+
 def _f(a):
     a = np.ascontiguousarray(a, dtype=np.float32)
     return a, a.ctypes.data_as(_fp)

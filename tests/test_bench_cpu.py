@@ -7,6 +7,7 @@ import sys
 import textwrap
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
 
 
 def _run(args, env_extra=None, timeout=600):
@@ -53,8 +54,9 @@ def test_max_over_ranks_and_shards_with_gloo(tmp_path):
         dist.init_process_group("gloo")
         rank, world = dist.get_rank(), dist.get_world_size()
         ms = bench.max_over_ranks(10.0 + 5.0 * rank, dist, "cpu")   # rank 1 is the slow one
-        first, count = bench.shard_of(rank, world, bench.B_PER_GPU)
-        print(json.dumps({{"rank": rank, "ms": ms, "first": first, "count": count}}))
+        first, count = bench.shard_of(rank, world, bench.GLOBAL_BATCH)               # strong: the batch is split
+        wfirst, wcount = bench.shard_of(rank, world, bench.B_PER_GPU, "weak")        # weak: everyone runs it all
+        print(json.dumps({{"rank": rank, "ms": ms, "first": first, "count": count, "wfirst": wfirst, "wcount": wcount}}))
         dist.destroy_process_group()
     """))
     procs = []
@@ -67,4 +69,14 @@ def test_max_over_ranks_and_shards_with_gloo(tmp_path):
     assert all(p.returncode == 0 for p in procs), [o[1][-500:] for o in outs]
     res = sorted((json.loads(o[0].strip().splitlines()[-1]) for o in outs), key=lambda d: d["rank"])
     assert [d["ms"] for d in res] == [15.0, 15.0]          # both ranks see the slowest rank's time
-    assert [d["first"] for d in res] == [0, 256] and all(d["count"] == 256 for d in res)
+    assert [d["first"] for d in res] == [0, 128] and all(d["count"] == 128 for d in res)
+    assert [d["wfirst"] for d in res] == [0, 256] and all(d["wcount"] == 256 for d in res)
+
+
+def test_strong_shards_cover_the_global_batch_exactly():
+    import bench
+    for world in (1, 2, 3, 4, 8):
+        shards = [bench.shard_of(r, world, 256) for r in range(world)]
+        assert shards[0][0] == 0 and sum(c for _, c in shards) == 256
+        for (f0, c0), (f1, _) in zip(shards, shards[1:]):
+            assert f0 + c0 == f1
