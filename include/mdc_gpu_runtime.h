@@ -84,8 +84,15 @@ void mgpuMemHostRegisterMemRef(int64_t rank, void *descriptor, int64_t elementSi
 void mgpuMemHostUnregister(void *ptr);
 void mgpuMemHostUnregisterMemRef(int64_t rank, void *descriptor, int64_t elementSizeBytes);
 
-/* lib/Runtime/CUDA/CudaRuntimeWrappers.cpp:297-299: device ordinal used by this thread. */
+/* lib/Runtime/CUDA/CudaRuntimeWrappers.cpp:297-299: device ordinal used by this thread.
+ * This is THE way to choose a GPU: every later runtime and op call of the thread works on that
+ * device (pool, streams, tensor maps, kernels).  A thread that never calls it adopts, at its
+ * first runtime call, the device that is current on it (the one cudaSetDevice chose, else
+ * ordinal 0).  Op entry points refuse to run (status set, nothing queued) while the thread's
+ * current CUDA device differs from the selected one, e.g. after a later cudaSetDevice.
+ * mgpuGetDefaultDevice (an addition) returns the selected ordinal, or -1 without a device. */
 void mgpuSetDefaultDevice(int32_t device);
+int32_t mgpuGetDefaultDevice(void);
 
 /* lib/Runtime/CUDA/CudaRuntimeWrappers.cpp:303-384.  tensorMap points at a 128-byte
  * CUtensorMap; the enum arguments are the driver's CUtensorMap* enums passed as ints. */
@@ -127,6 +134,14 @@ void mgpuUnregisterConstant(void *hostPtr);
  * sizes[rank], strides[rank]) - and its own grid, which is ignored.  Operands must be
  * contiguous and of one size, otherwise the launch is refused with a status. */
 void mgpuModuleOverrideKernel(const char *pattern, const char *builtin, int32_t rank);
+/* The same for kernels in the argument form the reference's GPU pipeline really emits: it lowers
+ * generated kernels and their launches with bare pointers (lib/Pipelines/MLIRToGPU.cpp:162-165
+ * useBarePtrCallConv, :180-183 kernelBarePtrCallConv; the argument array is built from the launch
+ * operands at lib/Dialect/Device/IR/GPUOffloadingAttr.cpp:222-247), so the kernel receives one
+ * pointer per operand and nothing else; shapes are static and known only to the generated code.
+ * `elements` is the element count of every operand; 0 means "the launch's grid x block", for
+ * graphs whose one-thread-per-element launch covers the tensor exactly. */
+void mgpuModuleOverrideKernelBare(const char *pattern, const char *builtin, int64_t elements);
 void mgpuModuleClearOverrides(void);
 
 /* Pool introspection / control: bytes held from the driver, bytes handed out, and a call
@@ -134,6 +149,9 @@ void mgpuModuleClearOverrides(void);
 uint64_t mgpuPoolReservedBytes(void);
 uint64_t mgpuPoolInUseBytes(void);
 void mgpuPoolTrim(void);
+/* Free and total device memory of the selected device as the driver reports them
+ * (cudaMemGetInfo); sees every allocation of the process, the pool's included. */
+void mgpuMemGetInfo(uint64_t *freeBytes, uint64_t *totalBytes);
 
 /* Grid / block a caller should pass to mgpuLaunchKernel for a built-in elementwise kernel
  * over n elements (the kernels are grid-stride, so any launch shape is still correct). */

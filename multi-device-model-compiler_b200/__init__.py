@@ -76,7 +76,10 @@ RUNTIME_SIGNATURES = {
     "mgpuTensorMapEncodeTiled": (None, [_vp, C.c_int, _u32, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int]),
     "mgpuTensorMapEncodeTiledMemref": (_vp, [_i64, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp]),
     "mgpuModuleOverrideKernel": (None, [C.c_char_p, C.c_char_p, _i32]),
+    "mgpuModuleOverrideKernelBare": (None, [C.c_char_p, C.c_char_p, _i64]),
     "mgpuModuleClearOverrides": (None, []),
+    "mgpuGetDefaultDevice": (_i32, []),
+    "mgpuMemGetInfo": (None, [C.POINTER(_u64), C.POINTER(_u64)]),
     "mgpuGetLastError": (_i32, []),
     "mgpuGetLastErrorString": (C.c_char_p, []),
     "mgpuClearLastError": (None, []),

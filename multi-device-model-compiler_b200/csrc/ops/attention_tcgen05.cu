@@ -131,6 +131,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Att
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  pdl_launch_dependents();  // after this CTA holds its tensor memory (see the Gemm kernel)
   pdl_wait();  // set-up above overlaps the previous kernel's tail; QKV is read below
 
   if (warp == 4) {

@@ -109,6 +109,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const conv::Para
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  pdl_launch_dependents();  // after this CTA holds its tensor memory (see the Gemm kernel)
   pdl_wait();
 
   if (warp < GATHER_WARPS) {

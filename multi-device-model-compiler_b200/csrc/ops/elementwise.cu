@@ -54,6 +54,19 @@ const DeviceInfo &device_info() {
     info = DeviceInfo();
     return info;
   }
+  // Everything the runtime library hands out (pool blocks, streams, tensor maps) belongs to the
+  // device it selected for this thread; an op queued while another device is current would
+  // mix the two.  Refuse instead: devices are chosen with mgpuSetDefaultDevice.
+  const int rt_dev = mgpuGetDefaultDevice();
+  if (rt_dev >= 0 && rt_dev != dev) {
+    char msg[160];
+    snprintf(msg, sizeof(msg),
+             "the thread's current CUDA device (%d) is not the device the runtime selected for it (%d); "
+             "choose devices with mgpuSetDefaultDevice", dev, rt_dev);
+    fail(msg);
+    info = DeviceInfo();
+    return info;
+  }
   if (info.ok && info.device == dev) return info;  // cached for the thread's current device
   info = DeviceInfo();
   cudaDeviceProp p;
@@ -106,6 +119,7 @@ __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <typename T16>
 __global__ void __launch_bounds__(kEwBlock)
 cast_f32_to_16(const float *__restrict__ src, T16 *__restrict__ dst, int64_t n) {
+  pdl_launch_dependents();
   pdl_wait();
   const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
   const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;

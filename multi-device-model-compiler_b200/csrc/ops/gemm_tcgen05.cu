@@ -72,19 +72,7 @@ struct GemmParams {
   int bn;         // tile width in output columns: 256, 192 or 128 (accumulators stay 256 TMEM columns apart)
   int cw;         // columns per staged output chunk: 64 (16-bit output, 128-byte rows) or 32
   uint32_t *err;
-#ifdef MDC_GEMM_TRACE
-  unsigned long long *trace;  // [grid][8] cycle counters (debug builds only)
-#endif
 };
-
-#ifdef MDC_GEMM_TRACE
-#define TRACE_T0() const long long _t0 = clock64()
-#define TRACE_ADD(slot) \
-  if (p.trace) atomicAdd(p.trace + blockIdx.x * 8 + (slot), (unsigned long long)(clock64() - _t0))
-#else
-#define TRACE_T0()
-#define TRACE_ADD(slot)
-#endif
 
 template <typename TOut>
 __device__ __forceinline__ void store_out8(TOut *dst, const float *v);
@@ -208,9 +196,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef MDC_GEMM_TRACE
-  const unsigned long long trace_c0 = clock64(), trace_t0 = ptx::globaltimer_ns();
-#endif
   // CG == 2: the two CTAs of a cluster work on one 256-row tile; rank 0 leads
   const int cta_rank = CG == 2 ? static_cast<int>(cluster_ctarank()) : 0;
   const bool leader = cta_rank == 0;
@@ -253,6 +238,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if constexpr (CG == 2) cluster_sync_all();  // the peer's barriers exist before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
+  // Only now, with this CTA's tensor memory allocated, may the next kernel of the chain be set
+  // up: a dependent CTA that shared the SM and took tensor-memory columns first would wait for
+  // this grid while this CTA waited for its columns.
+  pdl_launch_dependents();
   pdl_wait();  // everything above overlaps the previous kernel's tail; operands are read below
 
   if (warp == 0) {
@@ -264,13 +253,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int tile = worker; ok && tile < num_tiles; tile += num_workers) {
         const int m_blk = (tile / p.num_n_blocks) * CG + cta_rank, n_blk = tile % p.num_n_blocks;
         for (int kb = 0; kb < num_kb; ++kb) {
-          { TRACE_T0();
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
             atomicCAS(p.err, 0u, 0x10000000u | static_cast<uint32_t>(stage));
             ok = false;
             break;
           }
-          TRACE_ADD(0); }
           uint8_t *sa = tiles + stage * STAGE_BYTES;
           uint8_t *sb = sa + A_BYTES;
           if constexpr (CG == 2) {
@@ -299,22 +286,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = worker; ok && tile < num_tiles; tile += num_workers) {
-        { TRACE_T0();
         if (!mbar_wait(&acc_empty_bar[acc], acc_phase ^ 1, abort_flag)) {
           atomicCAS(p.err, 0u, 0x30000000u | static_cast<uint32_t>(acc));
           break;
         }
-        TRACE_ADD(1); }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          { TRACE_T0();
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
             atomicCAS(p.err, 0u, 0x20000000u | static_cast<uint32_t>(stage));
             ok = false;
             break;
           }
-          TRACE_ADD(2); }
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + stage * STAGE_BYTES);
           const uint64_t a_desc = make_smem_desc_sw128(sa, 16, 1024);
@@ -367,14 +350,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t acc_empty_addr1 = mapa_u32(smem_u32(&acc_empty_bar[1]), 0);
     for (int tile = worker; tile < num_tiles; tile += num_workers) {
       const int m_blk = (tile / p.num_n_blocks) * CG + cta_rank, n_blk = tile % p.num_n_blocks;
-      { TRACE_T0();
       if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag)) {
         atomicCAS(p.err, 0u, 0x40000000u | static_cast<uint32_t>(acc));
         break;
       }
-      if (threadIdx.x == 64) { TRACE_ADD(3); } }
       tc_fence_after();
-      TRACE_T0();
       if (p.tma_epi) {
         // ---- staged path.  The warp owns 32 rows x 128 accumulator columns, read from TMEM in
         // four 32-column pieces; the load of the next piece is in flight while this one goes
@@ -536,18 +516,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tc_fence_before();
       if constexpr (CG == 2) mbar_arrive_cluster(acc ? acc_empty_addr1 : acc_empty_addr0);
       else mbar_arrive(&acc_empty_bar[acc]);
-      if (threadIdx.x == 64) { TRACE_ADD(4); }
       if ((acc ^= 1) == 0) acc_phase ^= 1;
     }
     if (lane == 0) tma_store_wait<0>();  // all staged output has left shared memory
   }
-#ifdef MDC_GEMM_TRACE
-  if (threadIdx.x == 0 && p.trace) {
-    p.trace[blockIdx.x * 8 + 5] = (unsigned long long)clock64() - trace_c0;       // SM cycles in the kernel
-    p.trace[blockIdx.x * 8 + 6] = ptx::globaltimer_ns() - trace_t0;               // nanoseconds in the kernel
-  }
-#endif
-
   // ------------------------------ teardown ------------------------------
   if (*abort_flag) {
     // a wait gave up: give copies still in flight time to land before the CTA retires
@@ -568,11 +540,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 // ---------------------------------------------------------------------------------------
-#ifdef MDC_GEMM_TRACE
-static unsigned long long *g_gemm_trace = nullptr;
-#endif
-// one status word per device ordinal (a process may drive several devices, one at a time)
+// The status word the tensor-core kernels write a give-up code into lives in the library
+// image (static device storage, zero when the module is loaded), one copy per GPU: no device
+// memory is allocated for it, so callers that must not allocate can use and read it too.  Host
+// code needs the word's device address, looked up once per device ordinal (a process may
+// drive several devices, one at a time).
 constexpr int kMaxDevices = 64;
+static __device__ uint32_t g_status_word;
 static uint32_t *g_err_slots[kMaxDevices] = {nullptr};
 static int current_device_index() {
   const int d = device_info().device;
@@ -582,8 +556,9 @@ static int current_device_index() {
 uint32_t *device_error_slot() {
   uint32_t *&slot = g_err_slots[current_device_index()];
   if (!slot) {
-    if (!check_cuda(cudaMalloc(&slot, sizeof(uint32_t)), "cudaMalloc(error slot)")) return nullptr;
-    check_cuda(cudaMemset(slot, 0, sizeof(uint32_t)), "cudaMemset(error slot)");
+    void *sym = nullptr;
+    if (!check_cuda(cudaGetSymbolAddress(&sym, g_status_word), "cudaGetSymbolAddress(status word)")) return nullptr;
+    slot = static_cast<uint32_t *>(sym);
   }
   return slot;
 }
@@ -710,23 +685,17 @@ static int gemm_grid(const GemmParams &p, int sms) {
   return static_cast<int>(workers * cg);
 }
 
-}  // namespace mdc
-
-using namespace mdc;
-
-MDC_API void mgpuMatmulEx16(const void *a, const void *w_nk, const float *bias, const void *residual,
-                            void *out, int64_t M, int64_t N, int64_t Kp, int32_t dtype,
-                            int32_t out_dtype, int32_t act, void *stream) {
-  if (M <= 0 || N <= 0) return;
+// The whole of mgpuMatmulEx16 after the argument checks: tile choice, tensor maps, launch.
+// Shared by every entry point that ends in this Gemm; allocates nothing.
+static void matmul16_launch(const char *who, const void *a, const void *w_nk, const float *bias, const void *residual,
+                            void *out, int64_t M, int64_t N, int64_t Kp, int32_t dtype, int32_t out_dtype,
+                            int32_t act, cudaStream_t s) {
   const DeviceInfo &di = device_info();
-  if (!di.ok) return;
-  if (!dtype_is16(dtype)) { fail("mgpuMatmulEx16: dtype must be F16 or BF16"); return; }
-  if (Kp <= 0 || (Kp & 7)) { fail("mgpuMatmulEx16: K must be a positive multiple of 8"); return; }
-  if (M > 0x7fffffff || N > 0x7fffffff || Kp > 0x7fffffff) { fail("mgpuMatmulEx16: shape too large"); return; }
-  if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(w_nk) & 15u)) {
-    fail("mgpuMatmulEx16: operands must be 16-byte aligned");
-    return;
-  }
+  char msg[160];
+  auto failf = [&](const char *what) {
+    snprintf(msg, sizeof(msg), "%s: %s", who, what);
+    fail(msg);
+  };
   uint32_t *err = device_error_slot();
   if (!err) return;
 
@@ -772,30 +741,41 @@ MDC_API void mgpuMatmulEx16(const void *a, const void *w_nk, const float *bias, 
   p.num_m_blocks = static_cast<int>((M + gemm::BM - 1) / gemm::BM);
   p.num_n_blocks = static_cast<int>((N + bn - 1) / bn);
   p.err = err;
-#ifdef MDC_GEMM_TRACE
-  p.trace = g_gemm_trace;
-#endif
   const int grid = gemm_grid(p, di.sms);
-  if (grid <= 0) { fail("mgpuMatmulEx16: too many tiles"); return; }
-  cudaStream_t s = as_stream(stream);
+  if (grid <= 0) { failf("too many tiles"); return; }
 
   if (dtype == MGPU_DTYPE_F16) {
     if (out_dtype == MGPU_DTYPE_F16) launch_gemm_act<__half, __half>(ta, tb, to, tr, p, grid, act, s);
     else if (out_dtype == MGPU_DTYPE_F32) launch_gemm_act<__half, float>(ta, tb, to, tr, p, grid, act, s);
-    else fail("mgpuMatmulEx16: output type must be the operand type or F32");
+    else failf("output type must be the operand type or F32");
   } else {
     if (out_dtype == MGPU_DTYPE_BF16) launch_gemm_act<__nv_bfloat16, __nv_bfloat16>(ta, tb, to, tr, p, grid, act, s);
     else if (out_dtype == MGPU_DTYPE_F32) launch_gemm_act<__nv_bfloat16, float>(ta, tb, to, tr, p, grid, act, s);
-    else fail("mgpuMatmulEx16: output type must be the operand type or F32");
+    else failf("output type must be the operand type or F32");
   }
 }
+}  // namespace mdc
 
-#ifdef MDC_GEMM_TRACE
-MDC_API void mgpuDebugSetGemmTrace(unsigned long long *buf) { g_gemm_trace = buf; }
-#endif
+using namespace mdc;
+
+MDC_API void mgpuMatmulEx16(const void *a, const void *w_nk, const float *bias, const void *residual,
+                            void *out, int64_t M, int64_t N, int64_t Kp, int32_t dtype,
+                            int32_t out_dtype, int32_t act, void *stream) {
+  if (M <= 0 || N <= 0) return;
+  const DeviceInfo &di = device_info();
+  if (!di.ok) return;
+  if (!dtype_is16(dtype)) { fail("mgpuMatmulEx16: dtype must be F16 or BF16"); return; }
+  if (Kp <= 0 || (Kp & 7)) { fail("mgpuMatmulEx16: K must be a positive multiple of 8"); return; }
+  if (M > 0x7fffffff || N > 0x7fffffff || Kp > 0x7fffffff) { fail("mgpuMatmulEx16: shape too large"); return; }
+  if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(w_nk) & 15u)) {
+    fail("mgpuMatmulEx16: operands must be 16-byte aligned");
+    return;
+  }
+  matmul16_launch("mgpuMatmulEx16", a, w_nk, bias, residual, out, M, N, Kp, dtype, out_dtype, act, as_stream(stream));
+}
 
 MDC_API uint32_t mgpuOpsCheckDeviceStatus(void *stream) {
-  uint32_t *err = device_error_slot();
+  uint32_t *err = device_error_slot();  // an address look-up; allocates nothing
   if (!err) return 0xffffffffu;
   uint32_t h = 0;
   if (!check_cuda(cudaMemcpyAsync(&h, err, sizeof(h), cudaMemcpyDeviceToHost, as_stream(stream)), "read device status"))
@@ -823,22 +803,25 @@ MDC_API uint32_t mgpuOpsCheckDeviceStatus(void *stream) {
 //
 // * The array is kNoAllocScratchBytes (16 MiB) of device memory per GPU that loads the
 //   library, held until the process exits whether the entry point is used or not.
-// * Limit: 256 + roundup256(M * Kp * 2) + roundup256(N * Kp * 2) <= 16 MiB with Kp = K rounded
+// * Limit: roundup256(M * Kp * 2) + roundup256(N * Kp * 2) <= 16 MiB with Kp = K rounded
 //   up to 8 (for example M x N x K = 1024 x 768 x 4096, or 2048 x 512 x 3072).  Larger problems are
 //   rejected with the sticky status set and nothing launched.
 // * The first call on a device looks the array's device address up
 //   (cudaGetSymbolAddress); make that first call before starting any stream capture.
 // * All calls on a device share the one array, which keeps whatever the last call left in
 //   it.  Everything a call reads from it is written by that call first (the padded operand
-//   copies and the status word), but two calls that overlap on the GPU (different streams
-//   without an ordering between them) race on it: order them.
-// * No cudaMalloc / cudaFree / pool call is made on this path.
+//   copies), but two calls that overlap on the GPU (different streams without an ordering
+//   between them) race on it: order them.
+// * While profiling is off (mgpuOpsProfileBegin creates CUDA events), no cudaMalloc /
+//   cudaFree / pool call and no other allocating routine runs on this path.  A kernel that
+//   gives up a bounded wait reports through the same status word as every other entry point
+//   (mgpuOpsCheckDeviceStatus, which allocates nothing either).
 // =========================================================================================
 namespace mdc {
 constexpr size_t kNoAllocScratchBytes = size_t(16) << 20;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 // host-side cache of the array's device address, per device ordinal
-static unsigned char *g_noalloc_ptr[64] = {nullptr};
+static unsigned char *g_noalloc_ptr[kMaxDevices] = {nullptr};
 
 void cast_rows_padded(const float *src, void *dst, int64_t R, int64_t C, int64_t Cp, int32_t dtype,
                       cudaStream_t s);
@@ -854,15 +837,15 @@ MDC_API void mgpuMatmulNoAlloc(float *input, float *weight, float *bias, float *
   const int64_t Kp = (K + 7) / 8 * 8;
   auto up256 = [](size_t b) { return (b + 255) / 256 * 256; };
   const size_t a_bytes = up256(static_cast<size_t>(M) * Kp * 2), w_bytes = up256(static_cast<size_t>(N) * Kp * 2);
-  if (256 + a_bytes + w_bytes > kNoAllocScratchBytes) {
+  if (a_bytes + w_bytes > kNoAllocScratchBytes) {
     char msg[200];
     snprintf(msg, sizeof(msg),
              "mgpuMatmulNoAlloc: %lld x %lld x %lld needs %zu bytes of scratch, the fixed array holds %zu",
-             (long long)M, (long long)N, (long long)K, 256 + a_bytes + w_bytes, kNoAllocScratchBytes);
+             (long long)M, (long long)N, (long long)K, a_bytes + w_bytes, kNoAllocScratchBytes);
     fail(msg);
     return;
   }
-  if (di.device < 0 || di.device >= 64) { fail("mgpuMatmulNoAlloc: device ordinal out of range"); return; }
+  if (di.device < 0 || di.device >= kMaxDevices) { fail("mgpuMatmulNoAlloc: device ordinal out of range"); return; }
   // set-up, once per device, with that device current: the array's name is only a host-side
   // handle; kernels need the address the runtime resolves for this device
   if (!g_noalloc_ptr[di.device]) {
@@ -871,50 +854,11 @@ MDC_API void mgpuMatmulNoAlloc(float *input, float *weight, float *bias, float *
     g_noalloc_ptr[di.device] = static_cast<unsigned char *>(sym);
   }
   unsigned char *base = g_noalloc_ptr[di.device];
-  uint32_t *status = reinterpret_cast<uint32_t *>(base);  // first 256 bytes: kernel status word
-  void *a16 = base + 256;
-  void *w16 = base + 256 + a_bytes;
+  void *a16 = base;
+  void *w16 = base + a_bytes;
   cudaStream_t s = as_stream(stream);
-  if (!check_cuda(cudaMemsetAsync(status, 0, 256, s), "cudaMemsetAsync(status)")) return;
   cast_rows_padded(input, a16, M, K, Kp, MGPU_DTYPE_F16, s);
   mgpuPackWeight(weight, w16, K, N, MGPU_DTYPE_F16, stream);
-
-  const int cta_group = choose_cta_group(M);
-  const int bn = choose_bn(M, N, cta_group, di.sms);
-  CUtensorMap ta, tb;
-  if (!encode_tmap_2d(&ta, a16, MGPU_DTYPE_F16, static_cast<uint64_t>(Kp), static_cast<uint64_t>(M),
-                      static_cast<uint64_t>(Kp) * 2, gemm::BK, gemm::BM) ||
-      !encode_tmap_2d(&tb, w16, MGPU_DTYPE_F16, static_cast<uint64_t>(Kp), static_cast<uint64_t>(N),
-                      static_cast<uint64_t>(Kp) * 2, gemm::BK, bn / cta_group))
-    return;
-  GemmParams p;
-  p.cta_group = cta_group;
-  p.bn = bn;
-  p.cw = 32;  // fp32 output: 32 columns per 128-byte staged row
-  p.M = static_cast<int>(M);
-  p.N = static_cast<int>(N);
-  p.K = static_cast<int>(Kp);
-  p.bias = bias;
-  p.residual = nullptr;
-  p.out = output;
-  p.out_vec_ok = (N % 8 == 0) && !(reinterpret_cast<uintptr_t>(output) & 15u);
-  p.bias_vec_ok = bias && !(reinterpret_cast<uintptr_t>(bias) & 15u);
-  p.tma_epi = p.out_vec_ok && (!bias || p.bias_vec_ok);
-  p.num_m_blocks = static_cast<int>((M + gemm::BM - 1) / gemm::BM);
-  p.num_n_blocks = static_cast<int>((N + bn - 1) / bn);
-  // the library's own status word if it exists already (so mgpuOpsCheckDeviceStatus sees a
-  // kernel that gave up), else the word at the head of the fixed array
-  uint32_t *lib_slot = g_err_slots[current_device_index()];
-  p.err = lib_slot ? lib_slot : status;
-#ifdef MDC_GEMM_TRACE
-  p.trace = nullptr;
-#endif
-  CUtensorMap to = ta, tr = ta;
-  if (p.tma_epi &&
-      !encode_tmap_2d_ex(&to, output, MGPU_DTYPE_F32, static_cast<uint64_t>(N), static_cast<uint64_t>(M),
-                         static_cast<uint64_t>(N) * 4, 32, 32, 128))
-    return;
-  const int grid = gemm_grid(p, di.sms);
-  if (grid <= 0) { fail("mgpuMatmulNoAlloc: too many tiles"); return; }
-  launch_gemm_act<__half, float>(ta, tb, to, tr, p, grid, MGPU_ACT_NONE, s);
+  matmul16_launch("mgpuMatmulNoAlloc", a16, w16, bias, nullptr, output, M, N, Kp, MGPU_DTYPE_F16, MGPU_DTYPE_F32,
+                  MGPU_ACT_NONE, s);
 }

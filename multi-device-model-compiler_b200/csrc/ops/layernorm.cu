@@ -112,6 +112,7 @@ layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residua
                       const float *__restrict__ gamma, const float *__restrict__ beta,
                       TIn *__restrict__ sum_out, TOut *__restrict__ y, float eps, int64_t m, int n) {
   constexpr int EPC = LnTraits<TIn>::EPC;
+  pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t total_warps = static_cast<int64_t>(gridDim.x) * kLnWarpsPerBlock;

@@ -89,6 +89,13 @@ inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, s
 // Blocks until the grid this one was made dependent on has completed and its writes are
 // visible; returns at once for a kernel launched without the attribute.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the NEXT kernel of the chain be set up now: once every CTA of this grid has executed
+// this (or exited), the dependent grid's CTAs are placed on whatever SM resources are free
+// and run their prologue (barrier init, tensor-memory allocation, descriptor prefetch) up to
+// their own pdl_wait(), which still holds them until this whole grid has finished and its
+// writes are visible.  Called first thing in every chain kernel, so nothing of the next
+// kernel's launch and set-up latency is left exposed between two kernels.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 #endif
 
 // Optional per-launch timing: while profiling is on (mgpuOpsProfileBegin), every launch

@@ -32,8 +32,20 @@
 
 namespace {
 
+// Device selection is per host thread.  mgpuSetDefaultDevice(k) is the supported way to choose
+// a GPU; a thread that never called it adopts the device that is current on it (the one a
+// plain cudaSetDevice chose, ordinal 0 otherwise) at its first runtime call, and the op
+// library refuses to run while the thread's current CUDA device differs from this one.
 thread_local int32_t g_default_device = 0;
+thread_local bool g_device_chosen = false;  // by mgpuSetDefaultDevice on this thread
 thread_local bool g_device_bound = false;
+
+// Guards the process-wide tables below (constants, parked streams / events, kernel handle
+// caches, overrides).  The calls that touch them are short; one mutex is enough.
+std::recursive_mutex g_state_mu;
+// Serialises the staged pageable-copy path (one pinned ring and one helper team per process);
+// a thread that finds it taken uses the driver's plain copy instead of waiting.
+std::mutex g_stage_mu;
 
 std::mutex g_err_mu;
 int32_t g_last_error = 0;
@@ -64,6 +76,11 @@ bool rt_ok(cudaError_t e, const char *what) {
 // Binds the calling thread to the default device's primary context on first use.
 bool ensure_device() {
   if (g_device_bound) return true;
+  if (!g_device_chosen) {
+    int cur = 0;
+    if (!RT_CHECK(cudaGetDevice(&cur))) return false;
+    g_default_device = cur;
+  }
   if (!RT_CHECK(cudaSetDevice(g_default_device))) return false;
   if (!RT_CHECK(cudaFree(nullptr))) return false;  // forces context creation
   g_device_bound = true;
@@ -152,8 +169,10 @@ std::unordered_map<CUfunction, int32_t> g_smem_limit;
 struct KernelOverride {
   std::string pattern;   // exact name, or a prefix followed by '*'
   std::string builtin;
-  int rank = 1, operands = 3;
+  int rank = 1, operands = 3;  // rank 0: bare-pointer arguments (one pointer per operand)
+  int64_t elements = 0;        // bare form: element count, 0 = grid x block of the launch
   CUfunction target = nullptr;
+  int target_device = -1;      // the device `target` was resolved on
 };
 std::vector<KernelOverride *> g_overrides;          // entries are never freed: they are handed out as handles
 std::unordered_set<const void *> g_override_handles;
@@ -183,6 +202,7 @@ struct Constant {
   int device = 0;
   void *dev = nullptr;
   cudaEvent_t uploaded = nullptr;
+  cudaEvent_t last_use = nullptr;  // recorded after every copy served from `dev`
 };
 std::unordered_map<const void *, Constant> g_constants;
 mdc::DevicePool g_pools[kMaxDevices];
@@ -325,6 +345,9 @@ bool staged_copy(void *dst, const void *src, size_t bytes, cudaStream_t s) {
   const bool up = sk == MemKind::PageableHost && dk == MemKind::Device;
   const bool down = sk == MemKind::Device && dk == MemKind::PageableHost;
   if (!up && !down) return false;
+  // one staged copy at a time in the process: a second thread takes the plain path
+  std::unique_lock<std::mutex> stage_lock(g_stage_mu, std::try_to_lock);
+  if (!stage_lock.owns_lock()) return false;
   StagingRing *ring = staging_ring();
   if (!ring) return false;
   CopyTeam &team = copy_team();
@@ -438,19 +461,25 @@ MDC_API void mgpuModuleUnload(void) {
 
 MDC_API mgpu_function_t mgpuModuleGetFunction(const char *name) {
   if (!name || !ensure_device() || !driver().ok) return nullptr;
-  auto cached = g_builtin_cache.find(name);
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
+  // a function handle belongs to the context it was resolved in: the cache is per device
+  const std::string key = std::to_string(g_default_device) + ":" + name;
+  auto cached = g_builtin_cache.find(key);
   if (cached != g_builtin_cache.end()) return cached->second;
   auto sym = builtin_symbols().find(name);
   if (sym != builtin_symbols().end()) {
     cudaFunction_t fn = nullptr;
     if (!RT_CHECK(cudaGetFuncBySymbol(&fn, sym->second))) return nullptr;
-    g_builtin_cache[name] = reinterpret_cast<CUfunction>(fn);
+    g_builtin_cache[key] = reinterpret_cast<CUfunction>(fn);
     return fn;
   }
   // a module kernel that the caller routed to a built-in one
   for (KernelOverride *o : g_overrides)
     if (!o->pattern.empty() && pattern_matches(o->pattern, name)) {
-      if (!o->target) o->target = reinterpret_cast<CUfunction>(mgpuModuleGetFunction(o->builtin.c_str()));
+      if (!o->target || o->target_device != g_default_device) {
+        o->target = reinterpret_cast<CUfunction>(mgpuModuleGetFunction(o->builtin.c_str()));
+        o->target_device = g_default_device;
+      }
       return o->target ? o : nullptr;
     }
   CUfunction function = nullptr;
@@ -470,15 +499,29 @@ MDC_API void mgpuLaunchKernel(mgpu_function_t function, intptr_t gridX, intptr_t
     return;
   }
   if (!ensure_device() || !driver().ok) return;
-  if (g_override_handles.count(function)) {
-    // The caller passes the generated kernel's arguments: per operand the expanded memref
-    // (allocated, aligned, offset, sizes[rank], strides[rank]).  The built-in takes the data
+  bool is_override;
+  {
+    std::lock_guard<std::recursive_mutex> lock(g_state_mu);
+    is_override = g_override_handles.count(function) != 0;
+  }
+  if (is_override) {
+    // The caller passes the generated kernel's own arguments.  The built-in takes the data
     // pointers and the element count and chooses its own launch shape.
+    //  * bare-pointer form (what the reference's GPU pipeline emits, lib/Pipelines/
+    //    MLIRToGPU.cpp:162-165,180-183: one pointer per operand, shapes static and known only
+    //    to the generated code): the element count comes from the registration, or from the
+    //    caller's grid x block when registered as 0;
+    //  * memref form: per operand (allocated, aligned, offset, sizes[rank], strides[rank]).
     const KernelOverride *o = static_cast<const KernelOverride *>(function);
     const int per = 3 + 2 * o->rank;
     void *ptrs[3] = {nullptr, nullptr, nullptr};
     int64_t n = 1;
-    for (int op = 0; op < o->operands; ++op) {
+    if (o->rank == 0) {
+      for (int op = 0; op < o->operands; ++op) ptrs[op] = *static_cast<void **>(params[op]);
+      n = o->elements > 0 ? o->elements
+                          : static_cast<int64_t>(gridX) * gridY * gridZ * blockX * blockY * blockZ;
+    }
+    for (int op = 0; o->rank > 0 && op < o->operands; ++op) {
       void **g = params + op * per;
       char *aligned = *static_cast<char **>(g[1]);
       const int64_t offset = *static_cast<int64_t *>(g[2]);
@@ -513,6 +556,7 @@ MDC_API void mgpuLaunchKernel(mgpu_function_t function, intptr_t gridX, intptr_t
   // 48 KiB and more than was already granted (the reference queries the device and sets
   // the attribute on every launch, CudaRuntimeWrappers.cpp:118-131).
   if (smem > 48 * 1024) {
+    std::lock_guard<std::recursive_mutex> lock(g_state_mu);
     auto it = g_smem_limit.find(fn);
     if (it == g_smem_limit.end() || it->second < smem) {
       if (!DRV_CHECK(driver().FuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES,
@@ -542,6 +586,7 @@ MDC_API void mgpuBuiltinLaunchShape(int64_t n, intptr_t *gridX, intptr_t *blockX
 // queued, which is harmless because whatever is submitted next is ordered behind it.
 MDC_API mgpu_stream_t mgpuStreamCreate(void) {
   if (!ensure_device()) return nullptr;
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
   ObjectCache &c = object_cache();
   if (!c.streams.empty()) {
     cudaStream_t s = c.streams.back();
@@ -554,6 +599,7 @@ MDC_API mgpu_stream_t mgpuStreamCreate(void) {
 }
 MDC_API void mgpuStreamDestroy(mgpu_stream_t stream) {
   if (!stream) return;
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
   ObjectCache &c = object_cache();
   if (c.streams.size() < kMaxParked) {
     c.streams.push_back(static_cast<cudaStream_t>(stream));
@@ -569,6 +615,7 @@ MDC_API void mgpuStreamWaitEvent(mgpu_stream_t stream, mgpu_event_t event) {
 }
 MDC_API mgpu_event_t mgpuEventCreate(void) {
   if (!ensure_device()) return nullptr;
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
   ObjectCache &c = object_cache();
   if (!c.events.empty()) {
     cudaEvent_t e = c.events.back();
@@ -589,6 +636,7 @@ MDC_API mgpu_event_t mgpuEventEnableTimeCreate(void) {
 }
 MDC_API void mgpuEventDestroy(mgpu_event_t event) {
   if (!event) return;
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
   ObjectCache &c = object_cache();
   cudaEvent_t e = static_cast<cudaEvent_t>(event);
   // only the plain (timing-disabled) events are parked; timing events are rare
@@ -638,6 +686,7 @@ MDC_API void mgpuMemcpy(void *dst, void *src, size_t sizeBytes, mgpu_stream_t st
   if (!ensure_device()) return;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // a registered host constant (model weights): served from its device-resident copy
+  std::unique_lock<std::recursive_mutex> state_lock(g_state_mu);
   if (!g_constants.empty()) {
     auto it = g_constants.find(src);
     if (it != g_constants.end() && sizeBytes <= it->second.bytes && it->second.device == g_default_device) {
@@ -652,32 +701,51 @@ MDC_API void mgpuMemcpy(void *dst, void *src, size_t sizeBytes, mgpu_stream_t st
       }
       if (c.dev) {
         RT_CHECK(cudaMemcpyAsync(dst, c.dev, sizeBytes, cudaMemcpyDeviceToDevice, s));
+        // remembered so that the copy can be waited for before the block is given back
+        if (c.last_use) RT_CHECK(cudaEventRecord(c.last_use, s));
         return;
       }
     }
   }
+  state_lock.unlock();
   if (staged_copy(dst, src, sizeBytes, s)) return;
   RT_CHECK(cudaMemcpyAsync(dst, src, sizeBytes, cudaMemcpyDefault, s));
 }
 
 MDC_API void mgpuRegisterConstant(void *hostPtr, uint64_t sizeBytes) {
   if (!hostPtr || !sizeBytes || !ensure_device()) return;
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
   mgpuUnregisterConstant(hostPtr);
   Constant c;
   c.bytes = sizeBytes;
   c.device = g_default_device;
-  if (!RT_CHECK(cudaEventCreateWithFlags(&c.uploaded, cudaEventDisableTiming))) return;
+  if (!RT_CHECK(cudaEventCreateWithFlags(&c.uploaded, cudaEventDisableTiming)) ||
+      !RT_CHECK(cudaEventCreateWithFlags(&c.last_use, cudaEventDisableTiming)))
+    return;
   g_constants[hostPtr] = c;
 }
 
 MDC_API void mgpuUnregisterConstant(void *hostPtr) {
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
   auto it = g_constants.find(hostPtr);
   if (it == g_constants.end()) return;
-  if (it->second.dev) {
+  Constant &c = it->second;
+  if (c.dev) {
+    // the device copy may still be the source of copies queued on any stream: wait for the
+    // upload and for the last copy served from it, then give the block back to the pool of
+    // the device it came from
+    int cur = -1;
+    const bool switched = cudaGetDevice(&cur) == cudaSuccess && cur != c.device && cudaSetDevice(c.device) == cudaSuccess;
+    if (c.uploaded) cudaEventSynchronize(c.uploaded);
+    if (c.last_use) cudaEventSynchronize(c.last_use);
     cudaError_t e;
-    pool().free(it->second.dev, nullptr, &e);
+    const int d = (c.device >= 0 && c.device < kMaxDevices) ? c.device : 0;
+    g_pools[d].free(c.dev, nullptr, &e);
+    if (switched) cudaSetDevice(cur);
+    (void)cudaGetLastError();
   }
-  if (it->second.uploaded) cudaEventDestroy(it->second.uploaded);
+  if (c.uploaded) cudaEventDestroy(c.uploaded);
+  if (c.last_use) cudaEventDestroy(c.last_use);
   g_constants.erase(it);
 }
 MDC_API void mgpuMemset32(void *dst, unsigned int value, size_t count, mgpu_stream_t stream) {
@@ -721,6 +789,16 @@ MDC_API void mgpuMemHostUnregisterMemRef(int64_t /*rank*/, void *descriptor,
 MDC_API void mgpuSetDefaultDevice(int32_t device) {
   if (device != g_default_device) g_device_bound = false;
   g_default_device = device;
+  g_device_chosen = true;
+}
+
+MDC_API int32_t mgpuGetDefaultDevice(void) { return ensure_device() ? g_default_device : -1; }
+
+MDC_API void mgpuMemGetInfo(uint64_t *freeBytes, uint64_t *totalBytes) {
+  size_t f = 0, t = 0;
+  if (ensure_device()) RT_CHECK(cudaMemGetInfo(&f, &t));
+  if (freeBytes) *freeBytes = f;
+  if (totalBytes) *totalBytes = t;
 }
 
 MDC_API uint64_t mgpuPoolReservedBytes(void) { return pool().reserved_bytes(); }
@@ -779,31 +857,55 @@ MDC_API void *mgpuTensorMapEncodeTiledMemref(int64_t tensorRank, void *descripto
   return dmap;
 }
 
+namespace {
+int builtin_operands(const std::string &b) {
+  if (b == "mdc_add_f32") return 3;
+  if (b == "mdc_relu_f32" || b == "mdc_gelu_erf_f32" || b == "mdc_gelu_tanh_f32") return 2;
+  return 0;
+}
+void register_override(const char *pattern, const std::string &b, int rank, int operands, int64_t elements) {
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
+  for (KernelOverride *o : g_overrides)
+    if (o->pattern == pattern) {  // redefinition
+      o->builtin = b, o->rank = rank, o->operands = operands, o->elements = elements, o->target = nullptr;
+      return;
+    }
+  KernelOverride *o = new KernelOverride;
+  o->pattern = pattern, o->builtin = b, o->rank = rank, o->operands = operands, o->elements = elements;
+  g_overrides.push_back(o);
+  g_override_handles.insert(o);
+}
+}  // namespace
+
 MDC_API void mgpuModuleOverrideKernel(const char *pattern, const char *builtin, int32_t rank) {
   if (!pattern || !builtin || rank < 1 || rank > 8) {
     record_error(-1, "mgpuModuleOverrideKernel", "needs a pattern, a built-in kernel name and a rank of 1-8");
     return;
   }
   const std::string b = builtin;
-  int operands = 0;
-  if (b == "mdc_add_f32") operands = 3;
-  else if (b == "mdc_relu_f32" || b == "mdc_gelu_erf_f32" || b == "mdc_gelu_tanh_f32") operands = 2;
+  const int operands = builtin_operands(b);
   if (!operands) {
     record_error(-1, "mgpuModuleOverrideKernel", "the built-in must be mdc_add_f32, mdc_relu_f32, mdc_gelu_erf_f32 or mdc_gelu_tanh_f32");
     return;
   }
-  for (KernelOverride *o : g_overrides)
-    if (o->pattern == pattern) {  // redefinition
-      o->builtin = b, o->rank = rank, o->operands = operands, o->target = nullptr;
-      return;
-    }
-  KernelOverride *o = new KernelOverride;
-  o->pattern = pattern, o->builtin = b, o->rank = rank, o->operands = operands;
-  g_overrides.push_back(o);
-  g_override_handles.insert(o);
+  register_override(pattern, b, rank, operands, 0);
+}
+
+MDC_API void mgpuModuleOverrideKernelBare(const char *pattern, const char *builtin, int64_t elements) {
+  if (!pattern || !builtin || elements < 0) {
+    record_error(-1, "mgpuModuleOverrideKernelBare", "needs a pattern, a built-in kernel name and an element count >= 0");
+    return;
+  }
+  const int operands = builtin_operands(builtin);
+  if (!operands) {
+    record_error(-1, "mgpuModuleOverrideKernelBare", "the built-in must be mdc_add_f32, mdc_relu_f32, mdc_gelu_erf_f32 or mdc_gelu_tanh_f32");
+    return;
+  }
+  register_override(pattern, builtin, 0, operands, elements);
 }
 
 MDC_API void mgpuModuleClearOverrides(void) {
   // handles already given out stay valid objects; they only stop being matched
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
   for (KernelOverride *o : g_overrides) o->pattern.clear();
 }

@@ -217,3 +217,123 @@ def test_kernel_override_routes_a_generated_kernel_to_the_builtin(m, tmp_path):
     assert rt.mgpuGetLastError() != 0
     rt.mgpuClearLastError()
     rt.mgpuModuleUnload()
+
+
+# The same graph kernel in the argument form the reference's GPU pipeline really emits
+# (lib/Pipelines/MLIRToGPU.cpp:162-165,180-183: bare pointers): one pointer per operand and
+# nothing else, the static element count compiled into the code.
+def _bare_ptx(n, op="add.f32"):
+    return f"""
+.version 7.0
+.target sm_70
+.address_size 64
+
+.visible .entry main_graph_kernel(.param .u64 a, .param .u64 b, .param .u64 c)
+{{
+    .reg .pred p;
+    .reg .b32 r<5>;
+    .reg .b64 rd<12>;
+    .reg .f32 f<4>;
+    ld.param.u64 rd1, [a];
+    ld.param.u64 rd2, [b];
+    ld.param.u64 rd3, [c];
+    mov.u32 r1, %ctaid.x;
+    mov.u32 r2, %ntid.x;
+    mov.u32 r3, %tid.x;
+    mad.lo.s32 r4, r1, r2, r3;
+    cvt.u64.u32 rd5, r4;
+    setp.ge.u64 p, rd5, {n};
+    @p bra DONE;
+    cvta.to.global.u64 rd1, rd1;
+    cvta.to.global.u64 rd2, rd2;
+    cvta.to.global.u64 rd3, rd3;
+    shl.b64 rd6, rd5, 2;
+    add.s64 rd7, rd1, rd6;
+    add.s64 rd8, rd2, rd6;
+    add.s64 rd9, rd3, rd6;
+    ld.global.f32 f1, [rd7];
+    ld.global.f32 f2, [rd8];
+    {op} f3, f1, f2;
+    st.global.f32 [rd9], f3;
+DONE:
+    ret;
+}}
+"""
+
+
+def test_kernel_override_with_bare_pointer_arguments(m, tmp_path):
+    """A module kernel that SUBTRACTS, launched with the reference's bare-pointer argument
+    array; once overridden, the built-in Add must run on those three pointers, with the element
+    count taken from the registration or, when registered as 0, from the launch's grid x block."""
+    rt = m.runtime()
+    n = 3 * 640 * 64  # a multiple of the block, so grid x block covers it exactly
+    path = tmp_path / "ops.ptx"
+    path.write_text(_bare_ptx(n, "sub.f32"))
+    rng = np.random.default_rng(8)
+    a, b = rng.standard_normal(n).astype(np.float32), rng.standard_normal(n).astype(np.float32)
+    da, db, dc = m.to_device(a), m.to_device(b), m.DeviceBuffer(n * 4)
+    rt.mgpuModuleFileLoad(str(path).encode())
+    m.check("mgpuModuleFileLoad")
+    cells = [C.c_uint64(p) for p in (da.ptr, db.ptr, dc.ptr)]
+    params = (C.c_void_p * 3)(*[C.cast(C.pointer(c), C.c_void_p) for c in cells])
+
+    def launch(grid):
+        fn = rt.mgpuModuleGetFunction(b"main_graph_kernel")
+        assert fn
+        rt.mgpuMemset32(dc.ptr, 0x7FC00000, n, None)
+        rt.mgpuLaunchKernel(fn, grid, 1, 1, 256, 1, 1, 0, None, params, None)
+        rt.mgpuStreamSynchronize(None)
+        m.check("launch")
+        return m.to_host(dc, (n,), np.float32)
+
+    assert np.array_equal(launch(n // 256), a - b)               # the module's own kernel
+    rt.mgpuModuleOverrideKernelBare(b"main_graph_kernel", b"mdc_add_f32", n)
+    assert np.array_equal(launch(n // 256 + 7), a + b)           # count from the registration
+    rt.mgpuModuleOverrideKernelBare(b"main_graph_kernel", b"mdc_add_f32", 0)
+    assert np.array_equal(launch(n // 256), a + b)               # count from grid x block
+    rt.mgpuModuleClearOverrides()
+    assert np.array_equal(launch(n // 256), a - b)
+    rt.mgpuModuleOverrideKernelBare(b"x", b"no_such_builtin", 4)
+    assert rt.mgpuGetLastError() != 0
+    rt.mgpuClearLastError()
+    rt.mgpuModuleUnload()
+
+
+def test_pageable_copies_from_two_threads_at_once(m):
+    """Two host threads upload and download different 8 MiB pageable buffers on their own
+    streams at the same time: the staged-copy ring is one per process, so a second thread must
+    neither corrupt the first one's chunks nor hang."""
+    import threading
+    rt = m.runtime()
+    nbytes = 8 << 20
+    results, errors = {}, []
+
+    def worker(idx):
+        try:
+            rt.mgpuSetDefaultDevice(0)
+            rng = np.random.default_rng(100 + idx)
+            stream = rt.mgpuStreamCreate()
+            buf = rt.mgpuMemAlloc(nbytes, stream)
+            ok = True
+            for rep in range(6):
+                src = rng.integers(0, 256, nbytes, dtype=np.uint8)
+                dst = np.zeros(nbytes, np.uint8)
+                rt.mgpuMemcpy(buf, src.ctypes.data, nbytes, stream)
+                rt.mgpuMemcpy(dst.ctypes.data, buf, nbytes, stream)
+                rt.mgpuStreamSynchronize(stream)
+                ok = ok and np.array_equal(src, dst)
+            rt.mgpuMemFree(buf, stream)
+            rt.mgpuStreamDestroy(stream)
+            results[idx] = ok
+        except Exception as exc:  # noqa: BLE001
+            errors.append(exc)
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    assert not any(t.is_alive() for t in threads), "a copy thread is stuck"
+    assert not errors, errors
+    assert results == {0: True, 1: True}
+    m.check("threaded copies")

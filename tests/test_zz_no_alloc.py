@@ -6,6 +6,11 @@ It must give what mgpuMatmul gives, from a fixed scratch array inside the librar
 asking the device pool (or the driver) for memory, on repeated calls that reuse the array,
 and it must refuse problems larger than the array.  Collected last on purpose: a failure
 here cannot hide another test's result when a run stops at the first failure."""
+import os
+import subprocess
+import sys
+import textwrap
+
 import numpy as np
 import pytest
 
@@ -82,3 +87,48 @@ def test_sizes_beyond_the_fixed_array_are_rejected(m):
     msg = rt.mgpuGetLastErrorString().decode()
     assert "mgpuMatmulNoAlloc" in msg and "scratch" in msg
     rt.mgpuClearLastError()
+
+
+def test_first_library_call_in_a_fresh_process_and_no_driver_allocation():
+    """A process whose FIRST operator-library call is mgpuMatmulNoAlloc (no mgpuOpsInit, no
+    other op before it): the result must be right, the device status word must be readable
+    (and zero) although nothing ever allocated it, and a warmed call must leave the driver's
+    free-memory figure untouched, which also sees a direct cudaMalloc that the pool counters
+    cannot."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = textwrap.dedent(f"""
+        import ctypes as C, sys
+        import numpy as np
+        sys.path.insert(0, {root!r}); sys.path.insert(0, {os.path.join(root, "oracle")!r})
+        import __graft_entry__ as entry
+        import oracle
+        m = entry.load_package()
+        rt, ops = m.runtime(), m.ops()          # libraries loaded; mgpuOpsInit is NOT called
+        rng = np.random.default_rng(3)
+        M, N, K = 200, 136, 100
+        a = rng.standard_normal((M, K)).astype(np.float32)
+        w = (0.05 * rng.standard_normal((K, N))).astype(np.float32)
+        b = (0.05 * rng.standard_normal(N)).astype(np.float32)
+        da, dw, db, do = m.to_device(a), m.to_device(w), m.to_device(b), m.DeviceBuffer(M * N * 4)
+        assert ops.mgpuOpsLaunchCount() == 0
+        ops.mgpuMatmulNoAlloc(da.ptr, dw.ptr, db.ptr, do.ptr, M, N, K, None)   # the first op call
+        y = m.to_host(do, (M, N), np.float32)
+        assert ops.mgpuOpsCheckDeviceStatus(None) == 0
+        m.check("first call")
+        err = oracle.max_rel_err(oracle.matmul(a, w, b, round_mode=oracle.ROUND_F16), y)
+        assert err <= {TOL}, err
+        free0, free1, total = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        rt.mgpuStreamSynchronize(None)
+        rt.mgpuMemGetInfo(C.byref(free0), C.byref(total))
+        for _ in range(3):
+            ops.mgpuMatmulNoAlloc(da.ptr, dw.ptr, db.ptr, do.ptr, M, N, K, None)
+        rt.mgpuStreamSynchronize(None)
+        assert ops.mgpuOpsCheckDeviceStatus(None) == 0
+        rt.mgpuMemGetInfo(C.byref(free1), C.byref(total))
+        assert free0.value == free1.value, (free0.value, free1.value)
+        assert np.array_equal(m.to_host(do, (M, N), np.float32), y)
+        m.check("warmed calls")
+        print("NOALLOC_FRESH_OK")
+    """)
+    res = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=300, cwd=root)
+    assert res.returncode == 0 and "NOALLOC_FRESH_OK" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
