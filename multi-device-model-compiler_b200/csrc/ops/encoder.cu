@@ -173,7 +173,7 @@ static void run_stack(EncoderStack *st, const float *x_f32, const int32_t *seq_l
 
 static bool valid_config(int64_t L, int64_t d, int64_t F, int64_t H, int32_t act, int32_t dtype) {
   if (L <= 0 || d <= 0 || F <= 0 || H <= 0) { fail("encoder: sizes must be positive"); return false; }
-  if (d % H != 0 || d / H != 64) { fail("encoder: d_model / head_num must be 64"); return false; }
+  if (d % H != 0 || (d / H != 64 && d / H != 128)) { fail("encoder: d_model / head_num must be 64 or 128"); return false; }
   if (d % 8 || F % 8) { fail("encoder: d_model and feed_forward_dim must be multiples of 8"); return false; }
   if (!dtype_is16(dtype)) { fail("encoder: dtype must be F16 or BF16"); return false; }
   if (act < MGPU_ACT_NONE || act > MGPU_ACT_GELU_TANH) { fail("encoder: unknown activation"); return false; }

@@ -200,8 +200,32 @@ def test_reference_decoder_fixture(m, golden):
     assert np.max(np.abs(got - golden["dec_y"])) <= 2.0 * noise
 
 
-def test_head_dim_other_than_64_is_rejected(m, golden):
-    # the fixtures use head_dim 8; the tensor-core attention kernel requires 64 and must say so
+def test_layer_with_head_dim_128(m, capsys):
+    # the head geometry the reference layer is hard-wired for (8 heads x 128,
+    # lib/Kernels/GPU/LLM.cu:18-19) in the form it runs (pre-LN, causal, ReLU), through the
+    # legacy entry point
+    rng = np.random.default_rng(21)
+    B, S, d, F, H = 2, 256, 1024, 2048, 8
+    lw = make_layer(rng, d, F, std=0.02, bias_std=0.02)
+    lw["bqkv"] = None
+    x = rng.standard_normal((B, S, d)).astype(np.float32)
+    keys = ("wqkv", "wo", "bo", "w1", "b1", "w2", "b2")
+    dx = m.to_device(x)
+    dw = {k: m.to_device(lw[k]) for k in keys}
+    dy = m.DeviceBuffer(x.nbytes)
+    m.ops().mgpuLLMDecodingContextLayer(dx.ptr, dw["wqkv"].ptr, dw["wo"].ptr, dw["bo"].ptr, dw["w1"].ptr,
+                                        dw["b1"].ptr, dw["w2"].ptr, dw["b2"].ptr, dy.ptr, B, S, d, F, H,
+                                        True, True, True, None)
+    got = m.to_host(dy, x.shape, np.float32)
+    assert m.ops().mgpuOpsCheckDeviceStatus(None) == 0
+    m.check("mgpuLLMDecodingContextLayer")
+    ref = oracle.encoder_layer(x, lw, None, H, norm_first=True, causal=True, act=oracle.ACT_RELU,
+                               round_mode=oracle.ROUND_F16)
+    _check(ref, got, None, "legacy layer 8 heads x 128, pre-LN causal ReLU, fp16", capsys)
+
+
+def test_head_dim_other_than_64_or_128_is_rejected(m, golden):
+    # the small fixtures use head_dim 8; the tensor-core attention kernel requires 64 or 128 and must say so
     lw = {k: golden["enc_" + k] for k in ("wqkv", "bqkv", "wo", "bo", "w1", "b1", "w2", "b2", "ln1_g", "ln1_b", "ln2_g", "ln2_b")}
     with pytest.raises(m.MdcError):
         m.EncoderStack([lw], int(golden["enc_heads"]))
