@@ -123,6 +123,20 @@ void mgpuSetLastError(int32_t code, const char *what);
  * changing the buffer. */
 void mgpuRegisterConstant(void *hostPtr, uint64_t sizeBytes);
 void mgpuUnregisterConstant(void *hostPtr);
+/* What the op library builds on the constant cache (lowered graphs do not call these).
+ * mgpuConstantSourceOf(p): when the device block starting at p was last filled, whole, by an
+ * mgpuMemcpy from a registered constant (and has not since been freed or been the target of
+ * another mgpuMemcpy / mgpuMemset), the constant's host pointer; else NULL.  A kernel that
+ * writes into such a block is not seen: graphs do not modify their weight buffers.
+ * mgpuConstantDerived(key, tag, bytes, stream, &needsFill): a device buffer of `bytes` that
+ * lives as long as the registration of `key` (one per tag; e.g. the packed 16-bit form of a
+ * weight).  needsFill = 1: the caller must write it on `stream` and then call
+ * mgpuConstantDerivedReady(key, tag, stream); needsFill = 0: it is filled, and `stream` has
+ * been made to wait for that.  NULL when `key` is not a registered constant of this device. */
+const void *mgpuConstantSourceOf(const void *devPtr);
+void *mgpuConstantDerived(const void *hostKey, uint64_t tag, uint64_t bytes, mgpu_stream_t stream,
+                          int32_t *needsFill);
+void mgpuConstantDerivedReady(const void *hostKey, uint64_t tag, mgpu_stream_t stream);
 
 /* Kernel overrides.  The reference generates a scalar one-element-per-thread kernel for every
  * elementwise graph (lib/Dialect/Device/IR/GPUOffloadingAttr.cpp:255-313) and the lowered graph

@@ -86,6 +86,9 @@ RUNTIME_SIGNATURES = {
     "mgpuSetLastError": (None, [_i32, C.c_char_p]),
     "mgpuRegisterConstant": (None, [_vp, _u64]),
     "mgpuUnregisterConstant": (None, [_vp]),
+    "mgpuConstantSourceOf": (_vp, [_vp]),
+    "mgpuConstantDerived": (_vp, [_vp, _u64, _u64, _vp, C.POINTER(_i32)]),
+    "mgpuConstantDerivedReady": (None, [_vp, _u64, _vp]),
     "mgpuPoolReservedBytes": (_u64, []),
     "mgpuPoolInUseBytes": (_u64, []),
     "mgpuPoolTrim": (None, []),

@@ -384,15 +384,49 @@ MDC_API void mgpuTransformerEncoderLayer(const float *input, const float *qkv_we
                                          int64_t head_num, bool norm_first, bool causal, int32_t act,
                                          int32_t dtype, float eps, void *stream) {
   if (batch <= 0 || seq_len <= 0) return;
-  EncoderStack *st = static_cast<EncoderStack *>(
-      mgpuEncoderStackCreate(1, d_model, feed_forward_dim, head_num, norm_first, causal, act, dtype, eps));
-  if (!st) return;
-  mgpuEncoderStackSetLayer(st, 0, qkv_weight, qkv_bias, proj_weight, proj_bias, ffn1_weight, ffn1_bias,
-                           ffn2_weight, ffn2_bias, ln1_gamma, ln1_beta, ln2_gamma, ln2_beta, stream);
-  if (ensure_ws(st, batch * seq_len, stream)) run_stack(st, input, seq_lens, output, batch, seq_len, stream);
-  // everything the layer used goes back to the pool in stream order, as the reference does
-  // with its mgpuMemFreeAsync calls (LLM.cu:143-154)
-  destroy_stack(st, stream);
+  if (!device_info().ok) return;
+  if (!valid_config(1, d_model, feed_forward_dim, head_num, act, dtype)) return;
+  if (!qkv_weight || !proj_weight || !ffn1_weight || !ffn2_weight) { fail("mgpuTransformerEncoderLayer: weight matrices are required"); return; }
+  // A one-call stack that owns nothing but its workspace: biases and LayerNorm parameters are
+  // read where the caller has them, and a weight that is a copy of a registered constant
+  // comes packed from the constant cache (the reference re-casts all four weights on every
+  // call, LLM.cu:56-57,86-90,102-106,126-130); other weights are packed into pool blocks that
+  // go back in stream order, as the reference does with its temporaries (LLM.cu:143-154).
+  EncoderStack st;
+  st.layers_n = 1;
+  st.d = d_model;
+  st.F = feed_forward_dim;
+  st.H = head_num;
+  st.norm_first = norm_first;
+  st.causal = causal;
+  st.act = act;
+  st.dtype = dtype;
+  st.eps = eps;
+  st.layers.resize(1);
+  LayerWeights &lw = st.layers[0];
+  const int64_t d = d_model, F = feed_forward_dim;
+  bool cached[4] = {false, false, false, false};
+  lw.wqkv = packed_weight(qkv_weight, d, 3 * d, dtype, stream, &cached[0]);
+  lw.wo = packed_weight(proj_weight, d, d, dtype, stream, &cached[1]);
+  lw.w1 = packed_weight(ffn1_weight, d, F, dtype, stream, &cached[2]);
+  lw.w2 = packed_weight(ffn2_weight, F, d, dtype, stream, &cached[3]);
+  lw.bqkv = const_cast<float *>(qkv_bias);
+  lw.bo = const_cast<float *>(proj_bias);
+  lw.b1 = const_cast<float *>(ffn1_bias);
+  lw.b2 = const_cast<float *>(ffn2_bias);
+  lw.ln1_g = const_cast<float *>(ln1_gamma);
+  lw.ln1_b = const_cast<float *>(ln1_beta);
+  lw.ln2_g = const_cast<float *>(ln2_gamma);
+  lw.ln2_b = const_cast<float *>(ln2_beta);
+  if (lw.wqkv && lw.wo && lw.w1 && lw.w2) {
+    if (ensure_ws(&st, batch * seq_len, stream)) run_stack(&st, input, seq_lens, output, batch, seq_len, stream);
+  } else {
+    fail("mgpuTransformerEncoderLayer: out of device memory for the packed weights");
+  }
+  void *packed[4] = {lw.wqkv, lw.wo, lw.w1, lw.w2};
+  for (int i = 0; i < 4; ++i)
+    if (packed[i] && !cached[i]) mgpuMemFreeAsync(packed[i], stream);
+  free_ws(st.ws, stream);
 }
 
 // Legacy entry point: LayerNorm without affine, no QKV bias, full-length sequences, fp16.

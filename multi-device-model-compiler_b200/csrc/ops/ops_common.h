@@ -115,6 +115,10 @@ struct ProfileScope {
   }
 };
 
+// Packed 16-bit [N, Kp] form of an fp32 [K, N] weight, from the constant cache when the weight
+// is a copy of a registered constant (defined in ops_init.cu).
+void *packed_weight(const float *w, int64_t K, int64_t N, int32_t dtype, void *stream, bool *cached);
+
 // Device slot the tensor-core kernels write a non-zero code into when one of their bounded
 // waits gives up; checked (and turned into the status) by mgpuOpsCheckDeviceStatus().
 uint32_t *device_error_slot();

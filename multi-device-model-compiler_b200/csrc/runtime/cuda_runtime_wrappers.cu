@@ -19,6 +19,7 @@
 #include <thread>
 #include <unordered_map>
 #include <unordered_set>
+#include <iterator>
 #include <vector>
 
 #include <cuda.h>
@@ -203,8 +204,20 @@ struct Constant {
   void *dev = nullptr;
   cudaEvent_t uploaded = nullptr;
   cudaEvent_t last_use = nullptr;  // recorded after every copy served from `dev`
+  // buffers an op derived from this constant (e.g. a packed 16-bit copy of a weight), by tag
+  struct Derived {
+    void *dev = nullptr;
+    uint64_t bytes = 0;
+    cudaEvent_t ready = nullptr;  // recorded once the op has filled it
+    bool filled = false;
+  };
+  std::unordered_map<uint64_t, Derived> derived;
 };
 std::unordered_map<const void *, Constant> g_constants;
+// device buffers whose whole content is a copy of a registered constant: buffer -> host key.
+// Entered by mgpuMemcpy when it serves a copy from a constant into the START of a block,
+// dropped when the buffer is freed or is the destination of another copy or memset.
+std::unordered_map<const void *, const void *> g_copies_of_constants;
 mdc::DevicePool g_pools[kMaxDevices];
 mdc::DevicePool &pool() {
   int d = g_default_device;
@@ -669,6 +682,10 @@ MDC_API void *mgpuMemAlloc(uint64_t sizeBytes, mgpu_stream_t stream) {
 }
 MDC_API void mgpuMemFree(void *ptr, mgpu_stream_t stream) {
   if (!ptr) return;
+  {
+    std::lock_guard<std::recursive_mutex> lock(g_state_mu);
+    if (!g_copies_of_constants.empty()) g_copies_of_constants.erase(ptr);
+  }
   cudaError_t e;
   if (!pool().free(ptr, static_cast<cudaStream_t>(stream), &e)) {
     // not from the pool (e.g. a tensor map made by mgpuTensorMapEncodeTiledMemref)
@@ -703,10 +720,13 @@ MDC_API void mgpuMemcpy(void *dst, void *src, size_t sizeBytes, mgpu_stream_t st
         RT_CHECK(cudaMemcpyAsync(dst, c.dev, sizeBytes, cudaMemcpyDeviceToDevice, s));
         // remembered so that the copy can be waited for before the block is given back
         if (c.last_use) RT_CHECK(cudaEventRecord(c.last_use, s));
+        if (sizeBytes == c.bytes) g_copies_of_constants[dst] = src;
+        else g_copies_of_constants.erase(dst);
         return;
       }
     }
   }
+  if (!g_copies_of_constants.empty()) g_copies_of_constants.erase(dst);
   state_lock.unlock();
   if (staged_copy(dst, src, sizeBytes, s)) return;
   RT_CHECK(cudaMemcpyAsync(dst, src, sizeBytes, cudaMemcpyDefault, s));
@@ -744,17 +764,87 @@ MDC_API void mgpuUnregisterConstant(void *hostPtr) {
     if (switched) cudaSetDevice(cur);
     (void)cudaGetLastError();
   }
+  for (auto &kv : c.derived) {
+    Constant::Derived &dv = kv.second;
+    if (dv.ready) {
+      cudaEventSynchronize(dv.ready);
+      cudaEventDestroy(dv.ready);
+    }
+    if (dv.dev) {
+      // its users were queued on streams this library cannot enumerate: drain the device
+      cudaDeviceSynchronize();
+      cudaError_t e;
+      const int d = (c.device >= 0 && c.device < kMaxDevices) ? c.device : 0;
+      g_pools[d].free(dv.dev, nullptr, &e);
+    }
+  }
+  for (auto t = g_copies_of_constants.begin(); t != g_copies_of_constants.end();)
+    t = (t->second == hostPtr) ? g_copies_of_constants.erase(t) : std::next(t);
   if (c.uploaded) cudaEventDestroy(c.uploaded);
   if (c.last_use) cudaEventDestroy(c.last_use);
   g_constants.erase(it);
 }
+MDC_API const void *mgpuConstantSourceOf(const void *devPtr) {
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
+  if (g_copies_of_constants.empty()) return nullptr;
+  auto it = g_copies_of_constants.find(devPtr);
+  return it == g_copies_of_constants.end() ? nullptr : it->second;
+}
+
+MDC_API void *mgpuConstantDerived(const void *hostKey, uint64_t tag, uint64_t bytes, mgpu_stream_t stream,
+                                  int32_t *needsFill) {
+  if (needsFill) *needsFill = 0;
+  if (!hostKey || !bytes || !ensure_device()) return nullptr;
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
+  auto it = g_constants.find(hostKey);
+  if (it == g_constants.end() || it->second.device != g_default_device) return nullptr;
+  Constant::Derived &dv = it->second.derived[tag];
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dv.dev && dv.bytes != bytes) return nullptr;  // a tag names one size
+  if (!dv.dev) {
+    cudaError_t e;
+    dv.dev = pool().alloc(bytes, s, &e);
+    if (!dv.dev) {
+      rt_ok(e, "mgpuConstantDerived");
+      it->second.derived.erase(tag);
+      return nullptr;
+    }
+    dv.bytes = bytes;
+    if (!RT_CHECK(cudaEventCreateWithFlags(&dv.ready, cudaEventDisableTiming))) dv.ready = nullptr;
+  }
+  if (!dv.filled) {
+    if (needsFill) *needsFill = 1;
+  } else if (dv.ready) {
+    RT_CHECK(cudaStreamWaitEvent(s, dv.ready, 0));
+  }
+  return dv.dev;
+}
+
+MDC_API void mgpuConstantDerivedReady(const void *hostKey, uint64_t tag, mgpu_stream_t stream) {
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
+  auto it = g_constants.find(hostKey);
+  if (it == g_constants.end()) return;
+  auto dv = it->second.derived.find(tag);
+  if (dv == it->second.derived.end() || !dv->second.dev) return;
+  if (dv->second.ready) RT_CHECK(cudaEventRecord(dv->second.ready, static_cast<cudaStream_t>(stream)));
+  dv->second.filled = true;
+}
+
 MDC_API void mgpuMemset32(void *dst, unsigned int value, size_t count, mgpu_stream_t stream) {
   if (!ensure_device() || !driver().ok) return;
+  {
+    std::lock_guard<std::recursive_mutex> lock(g_state_mu);
+    if (!g_copies_of_constants.empty()) g_copies_of_constants.erase(dst);
+  }
   DRV_CHECK(driver().MemsetD32Async(reinterpret_cast<CUdeviceptr>(dst), value, count,
                                     reinterpret_cast<CUstream>(stream)));
 }
 MDC_API void mgpuMemset16(void *dst, unsigned short value, size_t count, mgpu_stream_t stream) {
   if (!ensure_device() || !driver().ok) return;
+  {
+    std::lock_guard<std::recursive_mutex> lock(g_state_mu);
+    if (!g_copies_of_constants.empty()) g_copies_of_constants.erase(dst);
+  }
   DRV_CHECK(driver().MemsetD16Async(reinterpret_cast<CUdeviceptr>(dst), value, count,
                                     reinterpret_cast<CUstream>(stream)));
 }

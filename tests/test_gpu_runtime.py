@@ -337,3 +337,45 @@ def test_pageable_copies_from_two_threads_at_once(m):
     assert not errors, errors
     assert results == {0: True, 1: True}
     m.check("threaded copies")
+
+
+def test_packed_weight_is_cached_for_copies_of_registered_constants(m):
+    """A lowered graph uploads its weights with mgpuMemcpy on every call.  Once the host buffer is
+    registered as a constant, mgpuMatmul packs the weight (cast + transpose) only the first time;
+    a buffer that has since been overwritten from elsewhere is packed afresh."""
+    import oracle
+    rt, ops = m.runtime(), m.ops()
+    rng = np.random.default_rng(12)
+    M, K, N = 96, 200, 136
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (0.05 * rng.standard_normal((K, N))).astype(np.float32)
+    w2 = (0.05 * rng.standard_normal((K, N))).astype(np.float32)
+    b = (0.05 * rng.standard_normal(N)).astype(np.float32)
+    da, db = m.to_device(a), m.to_device(b)
+    dw, do = m.DeviceBuffer(w.nbytes), m.DeviceBuffer(M * N * 4)
+    rt.mgpuRegisterConstant(w.ctypes.data, w.nbytes)
+
+    def call():
+        n0 = ops.mgpuOpsLaunchCount()
+        ops.mgpuMatmul(da.ptr, dw.ptr, db.ptr, do.ptr, M, N, K, None)
+        y = m.to_host(do, (M, N), np.float32)
+        m.check("mgpuMatmul")
+        return y, ops.mgpuOpsLaunchCount() - n0
+
+    rt.mgpuMemcpy(dw.ptr, w.ctypes.data, w.nbytes, None)       # upload (served from the constant cache)
+    assert rt.mgpuConstantSourceOf(dw.ptr) == w.ctypes.data
+    y1, launches1 = call()
+    rt.mgpuMemcpy(dw.ptr, w.ctypes.data, w.nbytes, None)       # the graph's next call uploads again
+    y2, launches2 = call()
+    assert launches2 == launches1 - 1                           # no pack kernel the second time
+    assert np.array_equal(y1, y2)
+    assert oracle.max_rel_err(oracle.matmul(a, w, b, round_mode=oracle.ROUND_F16), y2) <= 2e-2
+    # the same device buffer refilled from an ordinary host array: not a constant any more
+    rt.mgpuMemcpy(dw.ptr, w2.ctypes.data, w2.nbytes, None)
+    assert not rt.mgpuConstantSourceOf(dw.ptr)
+    y3, launches3 = call()
+    assert launches3 == launches1
+    assert oracle.max_rel_err(oracle.matmul(a, w2, b, round_mode=oracle.ROUND_F16), y3) <= 2e-2
+    rt.mgpuStreamSynchronize(None)
+    rt.mgpuUnregisterConstant(w.ctypes.data)
+    m.check("unregister")
