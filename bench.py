@@ -436,6 +436,9 @@ def main():
     x_all = np.random.default_rng(1).standard_normal((max(global_batch, max_batch), S, D)).astype(np.float32)
     x = np.ascontiguousarray(x_all[first:first + batch])
     x_weak = x_all[:max_batch]
+    # rank 0 re-computes the last rank's shard after the gather to check it bit for bit
+    lf, lc = shard_of(world - 1, world, args.batch, args.scaling)
+    x_last = np.ascontiguousarray(x_all[lf:lf + lc]) if (rank == 0 and world > 1 and args.scaling == "strong") else None
     del x_all
     stream = rt.mgpuStreamCreate()
     dx = mdc.to_device(x_weak, stream)
@@ -515,6 +518,43 @@ def main():
                 "note": "every rank runs 256 sequences (replicas); device-resident inputs"}
         rt.mgpuMemcpy(dx.ptr, x.ctypes.data, x.nbytes, stream)
         rt.mgpuStreamSynchronize(stream)
+
+    # ---------------- the one exchange of the path: the final gather of the output shards ----------------
+    gather_info = None
+    if world > 1 and args.scaling == "strong":
+        import torch
+        ops.mgpuEncoderStackRun(stack.h, dx.ptr, None, dy.ptr, batch, S, stream)
+        rt.mgpuStreamSynchronize(stream)
+        per = (global_batch + world - 1) // world  # equal-sized slots (the last shards may be shorter)
+        mine = torch.zeros((per, S, D), dtype=torch.float32, device=f"cuda:{local_rank}")
+        rt.mgpuMemcpy(mine.data_ptr(), dy.ptr, x.nbytes, stream)  # device to device
+        rt.mgpuStreamSynchronize(stream)
+        everyone = torch.empty((world * per, S, D), dtype=torch.float32, device=f"cuda:{local_rank}")
+        for _ in range(2):
+            dist.all_gather_into_tensor(everyone, mine)
+        torch.cuda.synchronize()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(args.steps):
+            dist.all_gather_into_tensor(everyone, mine)
+        g1.record()
+        torch.cuda.synchronize()
+        gather_ms = _max(g0.elapsed_time(g1)) / args.steps
+        gather_info = {"ms_per_step": gather_ms, "bytes_per_rank": int(mine.numel() * 4),
+                       "api": "torch.distributed.all_gather_into_tensor over NCCL",
+                       "note": "not part of `value`: the stack has no collective; this is the final output gather"}
+        if rank == 0:
+            # the last rank's shard, recomputed here: sharding must not change a single bit
+            dxl = mdc.to_device(x_last, stream)
+            dyl = mdc.DeviceBuffer(x_last.nbytes, stream)
+            ops.mgpuEncoderStackRun(stack.h, dxl.ptr, None, dyl.ptr, x_last.shape[0], S, stream)
+            mine_again = mdc.to_host(dyl, x_last.shape, np.float32, stream)
+            theirs = everyone[(world - 1) * per:(world - 1) * per + x_last.shape[0]].cpu().numpy()
+            gather_info["last_shard_bit_identical_to_rank0_recompute"] = bool(np.array_equal(mine_again, theirs))
+            dxl.release(stream)
+            dyl.release(stream)
+        del everyone, mine
 
     # ---------------- end to end through host buffers ----------------
     # (1) a stream of batches through SubmitHost / WaitHost: batch i+1 uploads while batch i
@@ -647,6 +687,8 @@ def main():
                 "hbm_kernels": hbm, "cpu_baseline": cpu}
         if weak is not None:
             line["weak"] = weak
+        if gather_info is not None:
+            line["gather"] = gather_info
         print(json.dumps(line), flush=True)
     stack.close()
     if dist is not None:

@@ -673,10 +673,38 @@ MDC_API float mgpuEventElapsedTime(mgpu_event_t begin, mgpu_event_t end) {
 }
 
 // ---------------- memory ----------------
+// Guard bands (MDC_POOL_GUARD=1, a debugging aid that stands in for a memory checker): every
+// block handed out is preceded and followed by kGuardBytes of a fixed pattern inside the same
+// pool block; mgpuMemFree reads both bands back (which synchronises the stream) and reports
+// an overwritten band through the sticky status, naming the block.  Out-of-range writes by a
+// kernel thus land in memory this library owns and are detected instead of corrupting a
+// neighbour silently.
+namespace {
+constexpr size_t kGuardBytes = 256;
+constexpr unsigned char kGuardPattern = 0xA5;
+bool guard_enabled() {
+  static const bool on = getenv("MDC_POOL_GUARD") && atoi(getenv("MDC_POOL_GUARD")) != 0;
+  return on;
+}
+std::unordered_map<const void *, uint64_t> g_guarded;  // user pointer -> user size
+}  // namespace
+
 MDC_API void *mgpuMemAlloc(uint64_t sizeBytes, mgpu_stream_t stream) {
   if (!ensure_device()) return nullptr;
   cudaError_t e;
-  void *p = pool().alloc(sizeBytes, static_cast<cudaStream_t>(stream), &e);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (guard_enabled()) {
+    const uint64_t user = (sizeBytes + 15) & ~uint64_t(15);
+    char *raw = static_cast<char *>(pool().alloc(user + 2 * kGuardBytes, s, &e));
+    rt_ok(e, "mgpuMemAlloc");
+    if (!raw) return nullptr;
+    RT_CHECK(cudaMemsetAsync(raw, kGuardPattern, kGuardBytes, s));
+    RT_CHECK(cudaMemsetAsync(raw + kGuardBytes + user, kGuardPattern, kGuardBytes, s));
+    std::lock_guard<std::recursive_mutex> lock(g_state_mu);
+    g_guarded[raw + kGuardBytes] = user;
+    return raw + kGuardBytes;
+  }
+  void *p = pool().alloc(sizeBytes, s, &e);
   rt_ok(e, "mgpuMemAlloc");
   return p;
 }
@@ -687,6 +715,39 @@ MDC_API void mgpuMemFree(void *ptr, mgpu_stream_t stream) {
     if (!g_copies_of_constants.empty()) g_copies_of_constants.erase(ptr);
   }
   cudaError_t e;
+  if (guard_enabled()) {
+    uint64_t user = 0;
+    bool known = false;
+    {
+      std::lock_guard<std::recursive_mutex> lock(g_state_mu);
+      auto it = g_guarded.find(ptr);
+      if (it != g_guarded.end()) {
+        user = it->second;
+        known = true;
+        g_guarded.erase(it);
+      }
+    }
+    if (known) {
+      cudaStream_t s = static_cast<cudaStream_t>(stream);
+      char *raw = static_cast<char *>(ptr) - kGuardBytes;
+      unsigned char bands[2 * kGuardBytes];
+      if (RT_CHECK(cudaMemcpyAsync(bands, raw, kGuardBytes, cudaMemcpyDeviceToHost, s)) &&
+          RT_CHECK(cudaMemcpyAsync(bands + kGuardBytes, raw + kGuardBytes + user, kGuardBytes, cudaMemcpyDeviceToHost, s)) &&
+          RT_CHECK(cudaStreamSynchronize(s))) {
+        for (size_t i = 0; i < 2 * kGuardBytes; ++i)
+          if (bands[i] != kGuardPattern) {
+            char msg[160];
+            snprintf(msg, sizeof(msg), "guard band %s block %p (%llu bytes) was overwritten at offset %zu",
+                     i < kGuardBytes ? "before" : "after", ptr, (unsigned long long)user, i % kGuardBytes);
+            record_error(-1, "mgpuMemFree", msg);
+            break;
+          }
+      }
+      pool().free(raw, s, &e);
+      rt_ok(e, "mgpuMemFree");
+      return;
+    }
+  }
   if (!pool().free(ptr, static_cast<cudaStream_t>(stream), &e)) {
     // not from the pool (e.g. a tensor map made by mgpuTensorMapEncodeTiledMemref)
     RT_CHECK(cudaFree(ptr));

@@ -379,3 +379,37 @@ def test_packed_weight_is_cached_for_copies_of_registered_constants(m):
     rt.mgpuStreamSynchronize(None)
     rt.mgpuUnregisterConstant(w.ctypes.data)
     m.check("unregister")
+
+
+def test_pool_guard_bands_catch_a_write_past_the_end():
+    """MDC_POOL_GUARD=1 (read once per process, hence the child process): a write that runs past
+    the end of a block lands in the guard band the pool keeps behind it, and freeing the block
+    reports it; well-behaved use stays silent and the encoder layer still gives the same result."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = textwrap.dedent(f"""
+        import sys
+        import numpy as np
+        sys.path.insert(0, {root!r})
+        import __graft_entry__ as entry
+        m = entry.load_package(); m.init(0)
+        rt = m.runtime()
+        a = np.arange(1000, dtype=np.float32)
+        good = m.to_device(a)
+        assert np.array_equal(m.add(a, a), a + a)            # ordinary use: no report
+        good.release()
+        assert rt.mgpuGetLastError() == 0
+        buf = rt.mgpuMemAlloc(4000, None)
+        rt.mgpuMemset32(buf, 0, 1001, None)                   # one element too many: into the band
+        rt.mgpuMemFree(buf, None)
+        assert rt.mgpuGetLastError() != 0
+        assert b"guard band after" in rt.mgpuGetLastErrorString()
+        rt.mgpuClearLastError()
+        print("GUARD_OK")
+    """)
+    env = dict(os.environ, MDC_POOL_GUARD="1")
+    res = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=300, env=env, cwd=root)
+    assert res.returncode == 0 and "GUARD_OK" in res.stdout, res.stdout[-1500:] + res.stderr[-1500:]
