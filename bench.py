@@ -62,6 +62,9 @@ def bytes_touched_per_step(batch):
 # residual, output) scaled and the weights kept.
 GEMM_DRAM_TRAFFIC = {
     # tokens: {shape: bytes}
+    32768: {"gemm_qkv": 53925888 + 96961536, "gemm_proj": 51560192 + 10394880,
+            "gemm_ffn1": 55139072 + 143000064, "gemm_ffn2": 206767872 + 37095936},
+    4096: {"gemm_qkv": 9883904, "gemm_proj": 7518208, "gemm_ffn1": 11096832, "gemm_ffn2": 29931520 + 1280},
 }
 
 
@@ -76,7 +79,7 @@ def gemm_traffic_per_launch(tokens):
     """Mean DRAM traffic of a Gemm launch of the step (bytes), or None without a capture."""
     if not GEMM_DRAM_TRAFFIC:
         return None
-    near = min(GEMM_DRAM_TRAFFIC, key=lambda k: abs(k - tokens))
+    near = min(GEMM_DRAM_TRAFFIC, key=lambda k: abs(np.log(k / max(tokens, 1))))
     table = GEMM_DRAM_TRAFFIC[near]
     if near == tokens:
         return sum(table.values()) / len(table)
@@ -291,6 +294,14 @@ def run_micro(args):
         out = mdc.DeviceBuffer(Bq * S * H * 64 * 2, stream)
         fn = lambda: ops.mgpuAttention(q.ptr, None, out.ptr, Bq, S, H, 64, False, mdc.F16, stream)
         work, unit = 4.0 * Bq * H * S * S * 64, "TFLOP/s"
+    elif name == "attention_d128":
+        # the head geometry of the reference layer (8 heads x 128, causal), sequences of 256
+        Sd, Hd, Dd = 256, 8, 128
+        Bq = max(tokens // Sd, 1)
+        q = mdc.to_device(rng.standard_normal((Bq * Sd, 3 * Hd * Dd)).astype(np.float16), stream)
+        out = mdc.DeviceBuffer(Bq * Sd * Hd * Dd * 2, stream)
+        fn = lambda: ops.mgpuAttention(q.ptr, None, out.ptr, Bq, Sd, Hd, Dd, True, mdc.F16, stream)
+        work, unit = 4.0 * Bq * Hd * Sd * Sd * Dd, "TFLOP/s"  # dense count (the causal half is skipped)
     elif name == "layernorm_f16":
         rows, n = tokens, args.hidden
         a = mdc.to_device(rng.standard_normal((rows, n)).astype(np.float16), stream)
@@ -346,7 +357,7 @@ def run_micro(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--micro", default=None, help="run one kernel only (for profiling): " + ", ".join(
-        list(MICRO) + ["matmul_c1_abi", "layer_c3", "attention", "attention_c3", "layernorm_f32", "layernorm_f16", "add_f32",
+        list(MICRO) + ["matmul_c1_abi", "layer_c3", "attention", "attention_c3", "attention_d128", "layernorm_f32", "layernorm_f16", "add_f32",
                      "maxpool_ref"] + list(CONV_MICRO)))
     ap.add_argument("--tokens", type=int, default=8192, help="--micro: rows / tokens of the small case")
     ap.add_argument("--hidden", type=int, default=768, help="--micro layernorm_f32 / add_f32: row length")
