@@ -127,9 +127,9 @@ void mgpuMatmulEx16(const void *a, const void *w_nk, const float *bias, const vo
  * P = softmax(q.k^T / sqrt(head_dim) + mask), mask = -inf for keys >= seq_lens[b] and, if
  * causal, keys after the query.  seq_lens (int32 [batch], device) may be NULL = all full.
  * head_dim must be 64 or 128 (128 is what the reference's own layer is built for,
- * lib/Kernels/GPU/LLM.cu:18-19).  Rows of padded queries are written (finite) but carry no
- * meaning; the qkv rows of padded positions are read (their scores are masked) and must hold
- * finite values. */
+ * lib/Kernels/GPU/LLM.cu:18-19).  Rows of padded queries are written (finite; zeros where a whole
+ * tile of 128 queries is padding) but carry no meaning; the qkv rows of padded positions are
+ * read (their scores are masked) and must hold finite values. */
 void mgpuAttention(const void *qkv, const int32_t *seq_lens, void *out, int64_t batch,
                    int64_t seq_len, int64_t heads, int64_t head_dim, bool causal, int32_t dtype,
                    mgpu_cuda_stream_t stream);

@@ -113,7 +113,8 @@ __device__ __forceinline__ AttnItem attn_item(const AttnParams &p, int item, int
   it.q0 = qt * attn::BQ;
   const int len = p.seq_lens ? min(max(p.seq_lens[it.b], 0), p.seq) : p.seq;
   it.kv_end = p.causal ? min(len, it.q0 + attn::BQ) : len;  // keys this query tile can see: [0, kv_end)
-  it.n_kv = (it.kv_end + attn::BKV - 1) / attn::BKV;
+  // a tile whose queries are all padding (q0 >= len) does no work: its rows are written as zeros
+  it.n_kv = it.q0 < len ? (it.kv_end + attn::BKV - 1) / attn::BKV : 0;
   return it;
 }
 
@@ -512,7 +513,8 @@ __device__ __forceinline__ AttnItem64 attn_item64(const AttnParams &p, int item,
   it.q0 = qt * attn64::BQ;
   const int len = p.seq_lens ? min(max(p.seq_lens[it.b], 0), p.seq) : p.seq;
   it.kv_end = p.causal ? min(len, it.q0 + attn64::BQ) : len;  // keys this query tile can see: [0, kv_end)
-  it.n_kv = (it.kv_end + attn64::BKV - 1) / attn64::BKV;
+  // a tile whose queries are all padding (q0 >= len) does no work: its rows are written as zeros
+  it.n_kv = it.q0 < len ? (it.kv_end + attn64::BKV - 1) / attn64::BKV : 0;
   return it;
 }
 

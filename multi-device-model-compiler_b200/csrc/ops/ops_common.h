@@ -115,6 +115,9 @@ struct ProfileScope {
   }
 };
 
+// fp32 [R, C] -> 16-bit [R, Cp] with zero padding of the columns C..Cp (elementwise.cu)
+void cast_rows_padded(const float *src, void *dst, int64_t R, int64_t C, int64_t Cp, int32_t dtype, cudaStream_t s);
+
 // Packed 16-bit [N, Kp] form of an fp32 [K, N] weight, from the constant cache when the weight
 // is a copy of a registered constant (defined in ops_init.cu).
 void *packed_weight(const float *w, int64_t K, int64_t N, int32_t dtype, void *stream, bool *cached);

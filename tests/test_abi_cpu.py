@@ -100,3 +100,38 @@ def test_bf16_helpers_round_to_nearest_even(built):
     ref = torch.from_numpy(x).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
     assert np.array_equal(bits, ref)
     assert np.array_equal(built.bf16_bits_to_f32(bits), torch.from_numpy(x).to(torch.bfloat16).float().numpy())
+
+
+_CXX_CALLER = r"""
+// what a sibling translation unit of the reference does (lib/Kernels/GPU/LLM.cu:50-158):
+// include the template declarations and call the instantiations the library exports
+#include "mdc_gpu_ops_cxx.h"
+void use(half *h, float *f, cudaStream_t s) {
+  invokeCudaCast<half, float>(h, f, 16, s);
+  invokeCudaCast<float, half>(f, h, 16, s);
+  mgpuMatmulEx<half>(h, h, h, h, h, 8, 8, 8, true, false, true, s);
+  mgpuMatmulEx<float>(f, f, f, f, f, 8, 8, 8, true, true, false, s);
+  mgpuLayerNorm<half>(h, h, h, h, 1e-5f, 4, 64, nullptr, s);
+  mgpuAddResidualPreLayerNorm<half>(h, h, h, h, h, h, 1e-5f, 4, 64, nullptr, s);
+  mgpuAddFusedQKVBiasTranspose<half>(h, h, h, h, h, 1, 4, 4, 2, 8, s);
+  gpuOpsInit(); gpuLLMOpsInit(); checkCudaStatus(cudaSuccess); gpuLLMOpsDeinit(); gpuOpsDeinit();
+}
+int main() { return 0; }
+"""
+
+
+def test_reference_style_cxx_caller_links_against_the_template_instantiations(built, tmp_path):
+    """A C++ caller that sees only the template DECLARATIONS (as the reference's other
+    translation units do, Kernels/GPU/Ops.h:51-74) must link: the library has to export the
+    explicit instantiations under their C++ names."""
+    src = tmp_path / "caller.cpp"
+    src.write_text(_CXX_CALLER)
+    exe = tmp_path / "caller"
+    lib_dir = os.path.dirname(built.OPS_LIB)
+    cmd = ["g++", "-std=c++17", "-I", os.path.join(ROOT, "include"), "-I", "/usr/local/cuda/include", str(src),
+           "-o", str(exe), "-L", lib_dir, "-lMultiDeviceGPUOps", "-lMultiDeviceCUDARuntime",
+           f"-Wl,-rpath,{lib_dir}"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-3000:]
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0
