@@ -239,8 +239,8 @@ CONV_MICRO = {
 
 
 def run_micro(args):
-    """One kernel, a few launches, on random data: the small case the ncu captures in
-    profiles/ are taken on.  Prints one JSON line with the CUDA-event time per launch."""
+    """One kernel, a few launches, on random data: the small case the ncu captures are taken
+    on.  Prints one JSON line with the CUDA-event time per launch."""
     import __graft_entry__ as entry
     mdc = entry.load_package()
     mdc.init(0)

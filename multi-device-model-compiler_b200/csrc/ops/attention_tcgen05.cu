@@ -74,17 +74,7 @@ struct AttnParams {
   int causal;
   float scale_log2e;  // log2(e) / sqrt(d)
   uint32_t *err;
-#ifdef MDC_ATTN_TRACE
-  unsigned long long *trace;
-#endif
 };
-#ifdef MDC_ATTN_TRACE
-#define TR_T0() long long _tr0 = clock64()
-#define TR_ADD(slot) { const long long _n = clock64(); if (p.trace) atomicAdd(p.trace + blockIdx.x * 16 + (slot), (unsigned long long)(_n - _tr0)); _tr0 = _n; }
-#else
-#define TR_T0()
-#define TR_ADD(slot)
-#endif
 
 template <typename T16>
 __device__ __forceinline__ uint32_t pack16(float a, float b);
@@ -175,9 +165,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
-#ifdef MDC_ATTN_TRACE
-  const long long tr_start = clock64();
-#endif
   pdl_launch_dependents();  // after this CTA holds its tensor memory (see the Gemm kernel)
   pdl_wait();  // set-up above overlaps the previous kernel's tail; QKV is read below
 
@@ -198,16 +185,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv,
         ++qn;
         for (int j = 0; j < it.n_kv; ++j, ++t) {
           const uint32_t st = t % KS, ph = ((t / KS) & 1) ^ 1;
-          TR_T0();
           if (!mbar_wait(&k_empty[st], ph, abort_flag)) { code = 0x72000000u | (t & 0xffff); break; }
-          TR_ADD(12);
           mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
 #pragma unroll
           for (int blk = 0; blk < C::BLOCKS; ++blk)
             tma_load_3d(sK + st * TILE_BYTES + blk * BLOCK_BYTES, &tmap_qkv, &k_full[st],
                         hd + it.head * HD + blk * 64, j * BKV, it.b);
           if (!mbar_wait(&v_empty[st], ph, abort_flag)) { code = 0x73000000u | (t & 0xffff); break; }
-          TR_ADD(13);
           mbar_arrive_expect_tx(&v_full[st], TILE_BYTES);
 #pragma unroll
           for (int blk = 0; blk < C::BLOCKS; ++blk)
@@ -234,9 +218,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv,
           const uint32_t st = t % KS, ph = (t / KS) & 1;
           // S = Q.K^T.  It overwrites the scores / P of the previous step, which the P.V issued
           // just before has finished reading by the time this executes (one in-order pipe).
-          TR_T0();
           if (!mbar_wait(&k_full[st], ph, abort_flag)) { code = 0x53000000u | (t & 0xffff); break; }
-          TR_ADD(8);
           tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < HD / 16; ++kk) {
@@ -248,11 +230,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv,
           umma_commit(&k_empty[st]);
           if (j == it.n_kv - 1) umma_commit(&q_empty[qs]);
           // O (+)= P.V, one N = 64 MMA group per 64 output columns
-          TR_ADD(11);
           if (!mbar_wait(&p_ready, t & 1, abort_flag)) { code = 0x55000000u | (t & 0xffff); break; }
-          TR_ADD(9);
           if (!mbar_wait(&v_full[st], ph, abort_flag)) { code = 0x56000000u | (t & 0xffff); break; }
-          TR_ADD(10);
           tc_fence_after();
 #pragma unroll
           for (int nb = 0; nb < C::BLOCKS; ++nb) {
@@ -338,18 +317,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv,
       // m_run is the reference point of the exponent (in score units), l_run the row sum
       float m_run = -INFINITY, l_run = 0.f;
       for (int j = 0; j < it.n_kv && ok; ++j, ++t) {
-        TR_T0();
         if (!mbar_wait(&s_full, t & 1, abort_flag)) {
           atomicCAS(p.err, 0u, 0x61000000u | (t & 0xffff));
           ok = false;
           break;
         }
-        if (r == 0) TR_ADD(0);
         tc_fence_after();
         // The MMAs complete in order: with these scores the previous item's last P.V has
         // completed as well, so its output can leave now.
         if (pending) write_pending();
-        if (r == 0) TR_ADD(5);
         // the whole row of scores: four loads in flight, one wait
         uint32_t s0[32], s1[32], s2[32], s3[32];
         tmem_ld_32x32(s_addr, s0);
@@ -366,7 +342,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv,
         tmem_ld_wait_regs(s1);
         tmem_ld_wait_regs(s2);
         tmem_ld_wait_regs(s3);
-        if (r == 0) TR_ADD(1);
         if (!full_tile) {
           // masked scores become -inf: they drop out of the maximum and give P = 0
 #pragma unroll
@@ -428,14 +403,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv,
         MDC_ATTN_P_PIECE(s3, 3)
 #undef MDC_ATTN_P_PIECE
         l_run += l_a + l_b;
-        if (r == 0) TR_ADD(2);
         // P (and a rescaled O) are in tensor memory and every S column of this tile has been read
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&p_ready);
-#ifdef MDC_ATTN_TRACE
-        if (r == 0) { TR_ADD(3); if (p.trace) atomicAdd(p.trace + blockIdx.x * 16 + 7, 1ull); }
-#endif
       }
       if (!ok) break;
       pending = true;
@@ -447,11 +418,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv,
       ++qn;
     }
     if (ok && pending) {
-      TR_T0();
       if (!mbar_wait(&all_done, 0, abort_flag)) {
         atomicCAS(p.err, 0u, 0x62000000u);
       } else {
-        if (r == 0) TR_ADD(4);
         tc_fence_after();
         write_pending();
       }
@@ -459,9 +428,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_qkv,
     if (lane == 0) tma_store_wait<0>();  // all staged output has left shared memory
   }
 
-#ifdef MDC_ATTN_TRACE
-  if (threadIdx.x == 0 && p.trace) p.trace[blockIdx.x * 16 + 6] = (unsigned long long)(clock64() - tr_start);
-#endif
   if (*abort_flag) {
     const unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) {
@@ -872,10 +838,6 @@ static void launch_attention(const CUtensorMap &tm, const CUtensorMap &tmo, cons
 
 using namespace mdc;
 
-#ifdef MDC_ATTN_TRACE
-static unsigned long long *g_attn_trace = nullptr;
-MDC_API void mgpuDebugSetAttnTrace(unsigned long long *buf) { g_attn_trace = buf; }
-#endif
 
 MDC_API void mgpuAttention(const void *qkv, const int32_t *seq_lens, void *out, int64_t batch,
                            int64_t seq_len, int64_t heads, int64_t head_dim, bool causal,
@@ -934,9 +896,6 @@ MDC_API void mgpuAttention(const void *qkv, const int32_t *seq_lens, void *out, 
   p.causal = causal ? 1 : 0;
   p.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(head_dim));
   p.err = err;
-#ifdef MDC_ATTN_TRACE
-  p.trace = g_attn_trace;
-#endif
   const int64_t n_items = q_tiles * heads * batch;
   if (n_items > 0x7fffffff) { fail("mgpuAttention: shape too large"); return; }
   cudaStream_t s = as_stream(stream);
