@@ -10,6 +10,7 @@
 // HBM bandwidth (8 bytes per element); the shorter 16-bit rows are bound by instruction issue,
 // which is why the statistics avoid anything costlier than adds and shuffles.
 #include "ops_common.h"
+#include "ptx_sm100.cuh"
 
 namespace mdc {
 
@@ -142,24 +143,31 @@ layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residua
   };
   fetch(row);
 
+  using ptx::F2;
+  using ptx::f2;
+  using ptx::f2_add;
+  using ptx::f2_fma;
+  using ptx::f2_get;
+  using ptx::f2_mul;
   for (; row < m;) {
-    float v[MAXI][EPC];
+    // the row as pairs of fp32 values: all arithmetic below is two lanes per instruction
+    // (add / mul / fma .f32x2), which halves the instruction count of this issue-bound kernel
+    F2 v[MAXI][EPC / 2];
 #pragma unroll
     for (int i = 0; i < MAXI; ++i) {
       const int c = lane + 32 * i;
-      if (FULL || c < nchunks) LnTraits<TIn>::unpack(raw[i], v[i]);
-    }
-    if constexpr (has_res) {
-#pragma unroll
-      for (int i = 0; i < MAXI; ++i) {
-        const int c = lane + 32 * i;
-        if (FULL || c < nchunks) {
+      if (FULL || c < nchunks) {
+        float t[EPC];
+        LnTraits<TIn>::unpack(raw[i], t);
+        if constexpr (has_res) {
           float r[EPC];
           LnTraits<TIn>::unpack(raw_res[i], r);
 #pragma unroll
-          for (int e = 0; e < EPC; ++e) v[i][e] = LnTraits<TIn>::round(v[i][e] + r[e]);
-          if (sum_out) store_vec<TIn, EPC>(sum_out + row * n + static_cast<int64_t>(c) * EPC, v[i]);
+          for (int e = 0; e < EPC; ++e) t[e] = LnTraits<TIn>::round(t[e] + r[e]);
+          if (sum_out) store_vec<TIn, EPC>(sum_out + row * n + static_cast<int64_t>(c) * EPC, t);
         }
+#pragma unroll
+        for (int e = 0; e < EPC / 2; ++e) v[i][e] = f2(t[2 * e], t[2 * e + 1]);
       }
     }
     // 16-bit rows are short: keep the next row's loads in flight during the reduction and
@@ -171,29 +179,37 @@ layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residua
     // exact two-pass statistics across the warp: the mean first (one butterfly), then the
     // centred sum of squares (a second one).  Every lane ends with the same bits, because the
     // two partners of a butterfly step add the same two numbers.
-    float sum = 0.f;
+    F2 sum2 = f2(0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < MAXI; ++i)
       if (FULL || lane + 32 * i < nchunks) {
 #pragma unroll
-        for (int e = 0; e < EPC; ++e) sum += v[i][e];
+        for (int e = 0; e < EPC / 2; ++e) sum2 = f2_add(sum2, v[i][e]);
       }
+    float sum_a, sum_b;
+    f2_get(sum2, sum_a, sum_b);
+    float sum = sum_a + sum_b;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
     const float mean = sum * inv_n;
-    float m2 = 0.f;
+    const F2 neg_mean = f2(-mean, -mean);
+    F2 m22 = f2(0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < MAXI; ++i)
       if (FULL || lane + 32 * i < nchunks) {
 #pragma unroll
-        for (int e = 0; e < EPC; ++e) {
-          v[i][e] -= mean;  // the centred value is what the output needs too
-          m2 = fmaf(v[i][e], v[i][e], m2);
+        for (int e = 0; e < EPC / 2; ++e) {
+          v[i][e] = f2_add(v[i][e], neg_mean);  // the centred value is what the output needs too
+          m22 = f2_fma(v[i][e], v[i][e], m22);
         }
       }
+    float m2_a, m2_b;
+    f2_get(m22, m2_a, m2_b);
+    float m2 = m2_a + m2_b;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) m2 += __shfl_xor_sync(0xffffffffu, m2, off);
     const float rstd = rsqrtf(fmaf(m2, inv_n, eps));
+    const F2 rstd2 = f2(rstd, rstd);
 
 #pragma unroll
     for (int i = 0; i < MAXI; ++i) {
@@ -202,13 +218,23 @@ layernorm_warp_kernel(const TIn *__restrict__ x, const TIn *__restrict__ residua
         float o[EPC];
 #pragma unroll
         for (int e4 = 0; e4 < EPC / 4; ++e4) {
-          float4 g = make_float4(1.f, 1.f, 1.f, 1.f), b = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (gamma) g = __ldg(reinterpret_cast<const float4 *>(gamma) + c * (EPC / 4) + e4);
-          if (beta) b = __ldg(reinterpret_cast<const float4 *>(beta) + c * (EPC / 4) + e4);
-          o[4 * e4 + 0] = fmaf(v[i][4 * e4 + 0] * rstd, g.x, b.x);
-          o[4 * e4 + 1] = fmaf(v[i][4 * e4 + 1] * rstd, g.y, b.y);
-          o[4 * e4 + 2] = fmaf(v[i][4 * e4 + 2] * rstd, g.z, b.z);
-          o[4 * e4 + 3] = fmaf(v[i][4 * e4 + 3] * rstd, g.w, b.w);
+          F2 y0 = f2_mul(v[i][2 * e4], rstd2), y1 = f2_mul(v[i][2 * e4 + 1], rstd2);
+          if (gamma && beta) {
+            const float4 g = __ldg(reinterpret_cast<const float4 *>(gamma) + c * (EPC / 4) + e4);
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(beta) + c * (EPC / 4) + e4);
+            y0 = f2_fma(y0, f2(g.x, g.y), f2(b.x, b.y));
+            y1 = f2_fma(y1, f2(g.z, g.w), f2(b.z, b.w));
+          } else if (gamma) {
+            const float4 g = __ldg(reinterpret_cast<const float4 *>(gamma) + c * (EPC / 4) + e4);
+            y0 = f2_mul(y0, f2(g.x, g.y));
+            y1 = f2_mul(y1, f2(g.z, g.w));
+          } else if (beta) {
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(beta) + c * (EPC / 4) + e4);
+            y0 = f2_add(y0, f2(b.x, b.y));
+            y1 = f2_add(y1, f2(b.z, b.w));
+          }
+          f2_get(y0, o[4 * e4 + 0], o[4 * e4 + 1]);
+          f2_get(y1, o[4 * e4 + 2], o[4 * e4 + 3]);
         }
         store_vec<TOut, EPC>(y + row * n + static_cast<int64_t>(c) * EPC, o);
       }
