@@ -186,6 +186,24 @@ def shard_of(rank, world, batch, scaling="strong"):
     return first, (rank + 1) * batch // world - first
 
 
+def pick_cpu_gemm(oracle, x, layers):
+    """The CPU arm should be the fastest this port can be: times one layer over a few sequences
+    with the oracle's own AVX2 loop and with cblas_sgemm of the OpenBLAS bundled with numpy
+    (when the wheel carries one) and keeps the faster (the name goes into `gemm_kernel`)."""
+    def once():
+        t0 = time.perf_counter()
+        oracle.encoder_stack(x, layers[:1], None, H, round_mode=oracle.ROUND_F16)
+        return time.perf_counter() - t0
+    oracle.use_blas(False)
+    once()
+    own = min(once(), once())
+    if oracle.use_blas(True):
+        once()
+        blas = min(once(), once())
+        if blas > own:
+            oracle.use_blas(False)
+
+
 def run_reference(args, rank, world):
     """The reference arm: the CPU restatement of the reference's path (oracle/), all host
     threads, on a bounded sample of the same workload per step."""
@@ -196,9 +214,9 @@ def run_reference(args, rank, world):
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import oracle
     sample = 16  # sequences per step (the full step is 256)
-    oracle.use_blas(True)  # the tuned library Gemm when the numpy wheel carries one
     layers = make_weights()
     x = np.random.default_rng(1).standard_normal((sample, S, D)).astype(np.float32)
+    pick_cpu_gemm(oracle, x[:8], layers)
     for _ in range(max(args.warmup, 0)):
         oracle.encoder_stack(x[:1], layers, None, H, round_mode=oracle.ROUND_F16)
     t0 = time.perf_counter()
@@ -668,7 +686,7 @@ def main():
         os.environ.setdefault("OMP_NUM_THREADS", str(os.cpu_count() or 1))
         oracle = entry.load_oracle()
         sample = min(64, batch)
-        oracle.use_blas(True)
+        pick_cpu_gemm(oracle, x[:8], layers)
         oracle.encoder_stack(x[:1], layers[:1], None, H, round_mode=oracle.ROUND_F16)  # warm the threads
         t0 = time.perf_counter()
         ref = oracle.encoder_stack(x[:sample], layers, None, H, round_mode=oracle.ROUND_F16)
