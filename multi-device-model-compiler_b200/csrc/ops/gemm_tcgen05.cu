@@ -347,7 +347,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t acc_empty_addr1 = mapa_u32(smem_u32(&acc_empty_bar[1]), 0);
     for (int tile = worker; tile < num_tiles; tile += num_workers) {
       const int m_blk = (tile / p.num_n_blocks) * CG + cta_rank, n_blk = tile % p.num_n_blocks;
-      if (!mbar_wait(&acc_full_bar[acc], acc_phase, abort_flag)) {
+      // one lane polls, the shuffle releases the others (256 threads would otherwise spin on the
+      // barrier word beside the tensor pipe for most of a mainloop)
+      if (!mbar_wait_warp(&acc_full_bar[acc], acc_phase, abort_flag)) {
         atomicCAS(p.err, 0u, 0x40000000u | static_cast<uint32_t>(acc));
         break;
       }
@@ -411,7 +413,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           act_fast_n<ACT, 32>(v);
           if (res) {
             if (sub_in_chunk == 0) {
-              if (!mbar_wait(&res_bar[ew], res_phase, abort_flag)) {
+              if (!mbar_wait_warp(&res_bar[ew], res_phase, abort_flag)) {
                 atomicCAS(p.err, 0u, 0x50000000u | static_cast<uint32_t>(ew));
                 chunk_ok = false;
                 break;
