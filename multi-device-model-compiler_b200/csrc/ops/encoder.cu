@@ -13,6 +13,7 @@
 // attention reads the packed QKV rows directly (no split / transpose kernel, the job of
 // lib/Kernels/GPU/Transpose.cu:6-85).  Activations between kernels are 16-bit, statistics
 // and accumulation fp32; the boundary is fp32 like the reference's.
+#include <cstdlib>
 #include <vector>
 
 #include "ops_common.h"
@@ -49,7 +50,24 @@ struct EncoderStack {
   // all runs of a stack share one activation workspace
   cudaEvent_t done_ev = nullptr;
   bool used = false;
+  // CUDA graphs of whole runs, keyed by the run's pointers and shape (see run_stack_replayed)
+  struct RunGraph {
+    const float *x = nullptr;
+    const int32_t *lens = nullptr;
+    float *y = nullptr;
+    int64_t B = 0, S = 0;
+    int seen = 0;                    // eager runs with this key so far
+    cudaGraphExec_t exec = nullptr;  // set once captured
+  };
+  std::vector<RunGraph> graphs;
+  bool graphs_off = false;  // a capture failed: stay eager
 };
+
+static void drop_graphs(EncoderStack *st) {
+  for (auto &g : st->graphs)
+    if (g.exec) cudaGraphExecDestroy(g.exec);
+  st->graphs.clear();
+}
 
 static void order_after_previous(EncoderStack *st, void *stream) {
   if (!st->done_ev) check_cuda(cudaEventCreateWithFlags(&st->done_ev, cudaEventDisableTiming), "event");
@@ -61,6 +79,7 @@ static void mark_run_done(EncoderStack *st, void *stream) {
 }
 
 static void free_ws(Workspace &w, void *stream) {
+  // (graphs captured over these buffers are dropped by the callers that own a stack)
   void **p[] = {&w.cur, &w.qkv, &w.att, &w.a, &w.n1, &w.f1};
   for (auto q : p) {
     if (*q) mgpuMemFreeAsync(*q, stream);
@@ -72,6 +91,7 @@ static void free_ws(Workspace &w, void *stream) {
 static bool ensure_ws(EncoderStack *st, int64_t tokens, void *stream) {
   Workspace &w = st->ws;
   if (w.tokens >= tokens) return true;
+  drop_graphs(st);  // they hold the old buffers' addresses
   free_ws(w, stream);
   const uint64_t T = static_cast<uint64_t>(tokens), d = st->d, F = st->F;
   w.cur = mgpuMemAllocAsync(T * d * 2, stream);
@@ -112,6 +132,7 @@ static void free_layer(LayerWeights &lw, void *stream) {
 
 static void destroy_stack(EncoderStack *st, void *stream) {
   if (!st) return;
+  drop_graphs(st);
   for (auto &lw : st->layers) free_layer(lw, stream);
   free_ws(st->ws, stream);
   for (int i = 0; i < 2; ++i) {
@@ -171,6 +192,85 @@ static void run_stack(EncoderStack *st, const float *x_f32, const int32_t *seq_l
   }
 }
 
+// A run whose pointers and shape have been seen before is replayed as a CUDA graph: the 85
+// launches of a 12-layer step (with their tensor-map encodes and launch attributes) cost the
+// host 0.5 - 2.7 ms per step, a graph launch a few microseconds, and the device gets the whole
+// chain, programmatic dependencies included, in one piece.  The first run with a key is eager
+// (it also does the one-time set-up that cannot be captured: function attributes, symbol
+// look-ups), the second is captured, later ones replay.  Not while profiling (per-kernel
+// events), not inside a caller's own capture; MDC_GRAPHS=0 turns it off.
+static bool graphs_enabled() {
+  static const bool on = !(getenv("MDC_GRAPHS") && atoi(getenv("MDC_GRAPHS")) == 0);
+  return on;
+}
+static void run_stack_replayed(EncoderStack *st, const float *x, const int32_t *lens, float *y, int64_t B, int64_t S,
+                               void *stream) {
+  cudaStream_t s = as_stream(stream);
+  bool eligible = graphs_enabled() && !st->graphs_off && !g_profiling && s != nullptr;
+  if (eligible) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+      (void)cudaGetLastError();
+      eligible = false;
+    }
+  }
+  if (!eligible) {
+    run_stack(st, x, lens, y, B, S, stream);
+    return;
+  }
+  EncoderStack::RunGraph *g = nullptr;
+  for (auto &c : st->graphs)
+    if (c.x == x && c.lens == lens && c.y == y && c.B == B && c.S == S) g = &c;
+  if (!g) {
+    if (st->graphs.size() >= 8) {  // a caller that keeps changing buffers: forget the oldest
+      if (st->graphs.front().exec) cudaGraphExecDestroy(st->graphs.front().exec);
+      st->graphs.erase(st->graphs.begin());
+    }
+    EncoderStack::RunGraph fresh;
+    fresh.x = x, fresh.lens = lens, fresh.y = y, fresh.B = B, fresh.S = S;
+    st->graphs.push_back(fresh);
+    g = &st->graphs.back();
+  }
+  if (g->exec) {
+    if (check_cuda(cudaGraphLaunch(g->exec, s), "cudaGraphLaunch")) {
+      g_launch_count.fetch_add(static_cast<uint64_t>(st->layers_n) * 7 + 1, std::memory_order_relaxed);
+      return;
+    }
+    st->graphs_off = true;
+    run_stack(st, x, lens, y, B, S, stream);
+    return;
+  }
+  if (g->seen++ == 0 || mgpuGetLastError() != 0) {
+    run_stack(st, x, lens, y, B, S, stream);
+    return;
+  }
+  // second run with this key: capture it, then launch what was captured
+  cudaGraph_t graph = nullptr;
+  if (cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+    (void)cudaGetLastError();
+    st->graphs_off = true;
+    run_stack(st, x, lens, y, B, S, stream);
+    return;
+  }
+  const uint64_t launches_before = g_launch_count.load(std::memory_order_relaxed);
+  run_stack(st, x, lens, y, B, S, stream);
+  const cudaError_t end = cudaStreamEndCapture(s, &graph);
+  g_launch_count.store(launches_before, std::memory_order_relaxed);  // captured, not yet launched
+  cudaGraphExec_t exec = nullptr;
+  if (end != cudaSuccess || !graph || mgpuGetLastError() != 0 ||
+      cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) {
+    (void)cudaGetLastError();
+    if (graph) cudaGraphDestroy(graph);
+    st->graphs_off = true;
+    if (mgpuGetLastError() == 0) run_stack(st, x, lens, y, B, S, stream);
+    return;
+  }
+  cudaGraphDestroy(graph);
+  g->exec = exec;
+  if (check_cuda(cudaGraphLaunch(exec, s), "cudaGraphLaunch"))
+    g_launch_count.fetch_add(static_cast<uint64_t>(st->layers_n) * 7 + 1, std::memory_order_relaxed);
+}
+
 static bool valid_config(int64_t L, int64_t d, int64_t F, int64_t H, int32_t act, int32_t dtype) {
   if (L <= 0 || d <= 0 || F <= 0 || H <= 0) { fail("encoder: sizes must be positive"); return false; }
   if (d % H != 0 || (d / H != 64 && d / H != 128)) { fail("encoder: d_model / head_num must be 64 or 128"); return false; }
@@ -214,6 +314,7 @@ MDC_API void mgpuEncoderStackSetLayer(void *stack, int64_t layer, const float *q
   if (!st || layer < 0 || layer >= st->layers_n) { fail("mgpuEncoderStackSetLayer: bad handle or layer index"); return; }
   if (!qkv_weight || !proj_weight || !ffn1_weight || !ffn2_weight) { fail("mgpuEncoderStackSetLayer: weight matrices are required"); return; }
   LayerWeights &lw = st->layers[static_cast<size_t>(layer)];
+  drop_graphs(st);  // captured runs hold the old weights' addresses
   free_layer(lw, stream);
   const int64_t d = st->d, F = st->F;
   lw.wqkv = pack(qkv_weight, d, 3 * d, st->dtype, stream);
@@ -237,7 +338,7 @@ MDC_API void mgpuEncoderStackRun(void *stack, const float *x, const int32_t *seq
   if (batch <= 0 || seq_len <= 0) return;
   order_after_previous(st, stream);
   if (!ensure_ws(st, batch * seq_len, stream)) return;
-  run_stack(st, x, seq_lens, y, batch, seq_len, stream);
+  run_stack_replayed(st, x, seq_lens, y, batch, seq_len, stream);
   mark_run_done(st, stream);
 }
 
@@ -269,6 +370,7 @@ static bool ensure_pipe(EncoderStack *st, int64_t per, int64_t seq_len) {
     cudaStreamSynchronize(st->s_out);
     const int64_t tokens = st->pipe_tokens > per * seq_len ? st->pipe_tokens : per * seq_len;
     const int64_t seqs = st->pipe_seqs > per ? st->pipe_seqs : per;
+    drop_graphs(st);
     for (int i = 0; i < 2; ++i) {
       if (st->x_dev[i]) mgpuMemFreeAsync(st->x_dev[i], st->s_comp);
       if (st->y_dev[i]) mgpuMemFreeAsync(st->y_dev[i], st->s_comp);
@@ -303,8 +405,8 @@ static void enqueue_host_chunk(EncoderStack *st, int set, const float *x_host, c
   cudaEventRecord(st->ev_in[set], st->s_in);
   cudaStreamWaitEvent(st->s_comp, st->ev_in[set], 0);
   if (st->slot_used[set]) cudaStreamWaitEvent(st->s_comp, st->ev_out[set], 0);  // y_dev[set] drained
-  run_stack(st, static_cast<const float *>(st->x_dev[set]), lens_host ? st->lens_dev[set] : nullptr,
-            static_cast<float *>(st->y_dev[set]), nb, seq_len, st->s_comp);
+  run_stack_replayed(st, static_cast<const float *>(st->x_dev[set]), lens_host ? st->lens_dev[set] : nullptr,
+                     static_cast<float *>(st->y_dev[set]), nb, seq_len, st->s_comp);
   cudaEventRecord(st->ev_comp[set], st->s_comp);
   mark_run_done(st, st->s_comp);
   cudaStreamWaitEvent(st->s_out, st->ev_comp[set], 0);
