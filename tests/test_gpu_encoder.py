@@ -230,3 +230,45 @@ def test_head_dim_other_than_64_or_128_is_rejected(m, golden):
     with pytest.raises(m.MdcError):
         m.EncoderStack([lw], int(golden["enc_heads"]))
     m.runtime().mgpuClearLastError()
+
+
+def test_legacy_layer_packs_registered_constant_weights_once(m):
+    """What a lowered graph does on every call: upload the weights with mgpuMemcpy, call
+    mgpuLLMDecodingContextLayer.  With the host weights registered as constants the four weight
+    packs (cast + transpose) run on the first call only, and the result does not change."""
+    rt, ops = m.runtime(), m.ops()
+    rng = np.random.default_rng(31)
+    B, S, d, F, H = 2, 128, 128, 256, 2
+    lw = make_layer(rng, d, F, std=0.05, bias_std=0.05)
+    keys = ("wqkv", "wo", "bo", "w1", "b1", "w2", "b2")
+    host = {k: np.ascontiguousarray(lw[k], dtype=np.float32) for k in keys}
+    x = rng.standard_normal((B, S, d)).astype(np.float32)
+    dx, dy = m.to_device(x), m.DeviceBuffer(x.nbytes)
+    dev = {k: m.DeviceBuffer(host[k].nbytes) for k in keys}
+    for k in ("wqkv", "wo", "w1", "w2"):
+        rt.mgpuRegisterConstant(host[k].ctypes.data, host[k].nbytes)
+
+    def call():
+        for k in keys:  # the graph's per-call weight upload
+            rt.mgpuMemcpy(dev[k].ptr, host[k].ctypes.data, host[k].nbytes, None)
+        n0 = ops.mgpuOpsLaunchCount()
+        ops.mgpuLLMDecodingContextLayer(dx.ptr, dev["wqkv"].ptr, dev["wo"].ptr, dev["bo"].ptr, dev["w1"].ptr,
+                                        dev["b1"].ptr, dev["w2"].ptr, dev["b2"].ptr, dy.ptr, B, S, d, F, H,
+                                        True, True, True, None)
+        y = m.to_host(dy, x.shape, np.float32)
+        assert ops.mgpuOpsCheckDeviceStatus(None) == 0
+        m.check("mgpuLLMDecodingContextLayer")
+        return y, ops.mgpuOpsLaunchCount() - n0
+
+    y1, n1 = call()
+    y2, n2 = call()
+    assert n2 == n1 - 4          # no weight pack on the second call
+    assert np.array_equal(y1, y2)
+    lw["bqkv"] = None
+    ref = oracle.encoder_layer(x, lw, None, H, norm_first=True, causal=True, act=oracle.ACT_RELU,
+                               round_mode=oracle.ROUND_F16)
+    _check(ref, y2, None)
+    rt.mgpuStreamSynchronize(None)
+    for k in ("wqkv", "wo", "w1", "w2"):
+        rt.mgpuUnregisterConstant(host[k].ctypes.data)
+    m.check("unregister")
