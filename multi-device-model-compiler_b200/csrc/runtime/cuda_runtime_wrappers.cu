@@ -450,6 +450,7 @@ MDC_API void mgpuSetLastError(int32_t code, const char *what) {
 // ---------------- module / launch ----------------
 MDC_API void mgpuModuleFileLoad(const char *fname) {
   if (!ensure_device() || !driver().ok) return;
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
   if (g_module) {
     DRV_CHECK(driver().ModuleUnload(g_module));
     g_module = nullptr;
@@ -466,6 +467,7 @@ MDC_API void mgpuModuleFileLoad(const char *fname) {
 }
 
 MDC_API void mgpuModuleUnload(void) {
+  std::lock_guard<std::recursive_mutex> lock(g_state_mu);
   if (g_module && driver().ok) {
     DRV_CHECK(driver().ModuleUnload(g_module));
     g_module = nullptr;
